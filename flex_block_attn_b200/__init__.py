@@ -1,0 +1,27 @@
+"""B200-native (sm_100a) block-sparse attention, drop-in for Tencent-Hunyuan/flex-block-attn's
+``flex_block_attn_func`` (same exported names as the reference's flex_block_attn/__init__.py:1-5)."""
+from .interface import (  # noqa: F401
+    FlexBlockAttnFunc,
+    SparseLists,
+    _flex_block_attn_backward,
+    _flex_block_attn_forward,
+    backward_with_lists,
+    build_index,
+    build_lists,
+    check_status,
+    flex_block_attn_func,
+    forward_with_lists,
+)
+
+__all__ = [
+    "flex_block_attn_func",
+    "_flex_block_attn_forward",
+    "_flex_block_attn_backward",
+    "FlexBlockAttnFunc",
+    "build_index",
+    "build_lists",
+    "forward_with_lists",
+    "backward_with_lists",
+    "check_status",
+    "SparseLists",
+]

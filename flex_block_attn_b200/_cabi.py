@@ -1,0 +1,83 @@
+"""ctypes binding of libfba_b200.so (declared in include/fba.h).
+
+This module is the only place that touches the C ABI.  It stands where the reference's
+``from flex_block_attn_cuda import attn_forward, attn_backward`` stood
+(reference flex_block_attn/flex_block_attn_interface.py:4).  There is no CPU fallback: if the
+library is missing or a call fails, a RuntimeError is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+
+_LIB = None
+LIB_PATH = Path(__file__).resolve().parent / "libfba_b200.so"
+
+EXPORTED_SYMBOLS = (
+    "fba_abi_version",
+    "fba_last_error",
+    "fba_build_index",
+    "fba_build_tile_lists",
+    "fba_fwd",
+    "fba_bwd_scratch_bytes",
+    "fba_bwd",
+)
+
+
+class FbaList(ctypes.Structure):
+    """Mirror of ``fba_list_t``."""
+
+    _fields_ = [
+        ("idx", ctypes.c_void_p),
+        ("cnt", ctypes.c_void_p),
+        ("msk", ctypes.c_void_p),
+        ("stride", ctypes.c_int32),
+        ("rows_per_bh", ctypes.c_int32),
+        ("bh_stride", ctypes.c_int32),
+        ("rows_div", ctypes.c_int32),
+        ("sub", ctypes.c_int32),
+    ]
+
+
+def lib() -> ctypes.CDLL:
+    """Load the shared library once (building it first when FBA_AUTO_BUILD=1 and it is missing)."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    if not LIB_PATH.exists() and os.environ.get("FBA_AUTO_BUILD", "0") == "1":
+        from .build import build_library
+
+        build_library()
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m flex_block_attn_b200.build` "
+            "(there is no CPU or PyTorch fallback for this operator)"
+        )
+    L = ctypes.CDLL(str(LIB_PATH))
+    vp, i32 = ctypes.c_void_p, ctypes.c_int
+    L.fba_abi_version.restype = i32
+    L.fba_abi_version.argtypes = []
+    L.fba_last_error.restype = ctypes.c_char_p
+    L.fba_last_error.argtypes = []
+    L.fba_build_index.restype = i32
+    L.fba_build_index.argtypes = [vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp]
+    L.fba_build_tile_lists.restype = i32
+    L.fba_build_tile_lists.argtypes = [vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp]
+    L.fba_fwd.restype = i32
+    L.fba_fwd.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, ctypes.POINTER(FbaList), vp, vp]
+    L.fba_bwd_scratch_bytes.restype = i32
+    L.fba_bwd_scratch_bytes.argtypes = [i32, i32, i32, ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]
+    L.fba_bwd.restype = i32
+    L.fba_bwd.argtypes = [vp] * 9 + [i32] * 5 + [ctypes.POINTER(FbaList), vp, vp, vp, vp]
+    if L.fba_abi_version() != 1:
+        raise RuntimeError("libfba_b200.so has an unexpected ABI version")
+    _LIB = L
+    return L
+
+
+def check(rc: int, what: str) -> None:
+    """Turn a non-zero status code into a RuntimeError carrying the library's message."""
+    if rc != 0:
+        msg = lib().fba_last_error().decode("utf-8", "replace")
+        raise RuntimeError(f"{what} failed with status {rc}: {msg}")

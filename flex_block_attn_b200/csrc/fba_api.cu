@@ -1,0 +1,67 @@
+// Error reporting, version query and TMA tensor-map construction for libfba_b200.so.
+#include <stdio.h>
+#include <string.h>
+
+#include "fba_internal.cuh"
+
+namespace fba {
+
+static thread_local char g_err[512] = "";
+
+int set_error(int code, const char* msg) {
+    snprintf(g_err, sizeof(g_err), "%s", msg ? msg : "");
+    return code;
+}
+
+int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) return FBA_OK;
+    snprintf(g_err, sizeof(g_err), "%s: %s", what, cudaGetErrorString(e));
+    return FBA_ERR_LAUNCH;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is resolved through the runtime so the library has no link-time
+// dependency on libcuda (it is built on machines without a driver).
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn) return fn;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !p) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+    return fn;
+}
+
+int make_tmap_bf16(CUtensorMap* out, const void* base, int seq, long long n_bh, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return set_error(FBA_ERR_DRIVER, "cuTensorMapEncodeTiled is not available");
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0)
+        return set_error(FBA_ERR_BAD_ARG, "tensor base address must be 16-byte aligned");
+    cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(seq), static_cast<cuuint64_t>(n_bh)};
+    cuuint64_t strides[2] = {128 * 2, static_cast<cuuint64_t>(seq) * 128 * 2};
+    cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        char buf[128];
+        snprintf(buf, sizeof(buf), "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+        return set_error(FBA_ERR_DRIVER, buf);
+    }
+    return FBA_OK;
+}
+
+}  // namespace fba
+
+extern "C" int fba_abi_version(void) { return FBA_ABI_VERSION; }
+extern "C" const char* fba_last_error(void) { return fba::g_err; }

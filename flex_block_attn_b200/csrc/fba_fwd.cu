@@ -1,0 +1,434 @@
+// Block-sparse attention forward for sm_100a.
+//
+// Computes what the reference's fwd_attend_ker (flex_block_attn_h100.cu:52-318) computes --
+// O = softmax(QK^T / sqrt(128) restricted to the active blocks) V and the row log-sum-exp -- but
+// is organised around Blackwell's tensor memory instead of Hopper register accumulators:
+//
+//   * a CTA owns two 128-row query tiles (A and B) of one (batch, head) and ping-pongs between
+//     them, so the tensor core works on one tile while the softmax warps work on the other;
+//   * one thread issues every tcgen05.mma.  S = Q K^T goes to TMEM (128 fp32 columns per tile),
+//     the softmax warps read it with tcgen05.ld (one thread = one row, so row max / row sum need
+//     no shuffles), write P back as bf16 into the same columns, and O += P V consumes P
+//     straight from TMEM; O (128 fp32 columns per tile) never leaves TMEM until the epilogue.
+//     TMEM columns: [0,128) S/P of tile A, [128,256) S/P of tile B, [256,384) O_A, [384,512) O_B;
+//   * one thread streams only the listed K / V tiles through a 5-stage shared-memory ring with
+//     TMA + mbarrier; the list comes from the compaction kernel, not from scanning the mask;
+//   * rescaling of O is lazy (only when the running row max grew by more than 2^8), done by the
+//     softmax warps between two MMAs of their tile.
+//
+// If both query tiles map to the same list row they share every K / V stage; otherwise each tile
+// streams its own list ("split" mode) in a fixed interleaving that loader and issuer both follow.
+#include "fba_common.cuh"
+
+namespace fba {
+
+constexpr int kFwdThreads = 320;  // warps 0-3 softmax A, 4-7 softmax B, 8 MMA issue, 9 TMA
+constexpr int kFwdStages = 5;
+constexpr uint32_t kFwdSmemQ = 0;
+constexpr uint32_t kFwdSmemRing = 2 * kTileBytes;
+constexpr uint32_t kFwdSmemBars = kFwdSmemRing + kFwdStages * kTileBytes;
+constexpr uint32_t kFwdSmemBytes = kFwdSmemBars + 256 + 1024;  // + alignment slack
+
+struct FwdParams {
+    ListDev list;
+    float* lse;
+    uint32_t* status;
+    int n_mtiles, Sq, Hq, Hkv;
+};
+
+// Barrier slots (8 bytes each) inside the barrier block.
+enum FwdBar : uint32_t {
+    kBarQFull = 0,                         // 2
+    kBarRingFull = 2,                      // kFwdStages
+    kBarRingEmpty = 2 + kFwdStages,        // kFwdStages
+    kBarSFull = 2 + 2 * kFwdStages,        // 2
+    kBarPReady = 4 + 2 * kFwdStages,       // 2
+    kBarODone = 6 + 2 * kFwdStages,        // 2
+    kBarCount = 8 + 2 * kFwdStages
+};
+
+__global__ void __launch_bounds__(kFwdThreads, 1)
+fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+               const FwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - raw);
+    const uint32_t bars = base + kFwdSmemBars;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + kFwdSmemBars + 8 * kBarCount);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + kFwdSmemBars + 8 * kBarCount + 4);
+    auto bar = [&](uint32_t slot) { return bars + 8u * slot; };
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int bh = blockIdx.y;
+    const int pair = blockIdx.x;
+    const int hr = p.Hq / p.Hkv;
+    const int bhk = (bh / p.Hq) * p.Hkv + (bh % p.Hq) / hr;
+
+    // Per-tile list rows and lengths (identical in every thread).
+    int mt[2] = {2 * pair, 2 * pair + 1};
+    long long lrow[2];
+    int n[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        const bool valid = mt[t] < p.n_mtiles;
+        lrow[t] = static_cast<long long>(bh) * p.list.bh_stride + (valid ? mt[t] / p.list.rows_div : 0);
+        n[t] = valid ? p.list.cnt[lrow[t]] * p.list.sub : 0;
+    }
+    const bool tile1_valid = mt[1] < p.n_mtiles;
+    const bool shared_mode = tile1_valid && lrow[0] == lrow[1];
+    const int sub = p.list.sub;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        mbar_init(bar(kBarQFull + 0), 1);
+        mbar_init(bar(kBarQFull + 1), 1);
+        for (int s = 0; s < kFwdStages; ++s) {
+            mbar_init(bar(kBarRingFull + s), 1);
+            mbar_init(bar(kBarRingEmpty + s), 1);
+        }
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(bar(kBarSFull + t), 1);
+            mbar_init(bar(kBarPReady + t), 128);
+            mbar_init(bar(kBarODone + t), 1);
+        }
+        mbar_fence_init();
+    }
+    if (warp == 8) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+        tmem_relinquish();
+    }
+    if (warp == 9 && lane == 0) {
+        tma_prefetch_desc(&tm_q);
+        tma_prefetch_desc(&tm_k);
+        tma_prefetch_desc(&tm_v);
+        tma_prefetch_desc(&tm_o);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t sQ[2] = {base + kFwdSmemQ, base + kFwdSmemQ + kTileBytes};
+    auto ring = [&](int s) { return base + kFwdSmemRing + static_cast<uint32_t>(s) * kTileBytes; };
+    auto kv_tile_of = [&](int t, int i) {
+        const int e = i / sub;
+        return p.list.idx[lrow[t] * p.list.stride + e] * sub + (i - e * sub);
+    };
+
+    if (warp == 9) {
+        // ------------------------------------------------------------------ TMA loader
+        if (lane == 0) {
+            bool ok = true;
+            uint32_t prod = 0;
+            for (int t = 0; t < 2; ++t) {
+                if (n[t] > 0) {
+                    mbar_expect_tx(bar(kBarQFull + t), kTileBytes);
+                    tma_load_3d(sQ[t], &tm_q, 0, mt[t] * 128, bh, bar(kBarQFull + t));
+                    tma_load_3d(sQ[t] + kPanelBytes, &tm_q, 64, mt[t] * 128, bh, bar(kBarQFull + t));
+                }
+            }
+            auto load = [&](const CUtensorMap* tm, int kv_tile, uint32_t tag) {
+                if (!ok) return;
+                const int s = prod % kFwdStages;
+                const uint32_t parity = ((prod / kFwdStages) & 1u) ^ 1u;
+                if (!mbar_wait(bar(kBarRingEmpty + s), parity, abort_flag)) {
+                    report_timeout(p.status, 1, 9, prod, tag);
+                    ok = false;
+                    return;
+                }
+                mbar_expect_tx(bar(kBarRingFull + s), kTileBytes);
+                tma_load_3d(ring(s), tm, 0, kv_tile * 128, bhk, bar(kBarRingFull + s));
+                tma_load_3d(ring(s) + kPanelBytes, tm, 64, kv_tile * 128, bhk, bar(kBarRingFull + s));
+                ++prod;
+            };
+            const int ln[2] = {n[0], shared_mode ? 0 : n[1]};
+            const int nmax = ln[0] > ln[1] ? ln[0] : ln[1];
+            for (int t = 0; t < 2; ++t)
+                if (ln[t] > 0) load(&tm_k, kv_tile_of(t, 0), 100 + t);
+            for (int i = 0; i < nmax && ok; ++i) {
+                for (int t = 0; t < 2; ++t) {
+                    if (i < ln[t]) {
+                        load(&tm_v, kv_tile_of(t, i), 200 + t);
+                        if (i + 1 < ln[t]) load(&tm_k, kv_tile_of(t, i + 1), 100 + t);
+                    }
+                }
+            }
+        }
+    } else if (warp == 8) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            bool ok = true;
+            uint32_t cons = 0;
+            const uint32_t tS[2] = {tmem + 0, tmem + 128};
+            const uint32_t tO[2] = {tmem + 256, tmem + 384};
+            auto acquire = [&](uint32_t tag) -> int {
+                const int s = cons % kFwdStages;
+                if (!mbar_wait(bar(kBarRingFull + s), (cons / kFwdStages) & 1u, abort_flag)) {
+                    report_timeout(p.status, 1, 8, cons, tag);
+                    ok = false;
+                }
+                ++cons;
+                return s;
+            };
+            int slot_k[2] = {0, 0}, slot_v[2] = {0, 0};
+            // Prologue: S(0) of both tiles.
+            for (int t = 0; t < 2 && ok; ++t) {
+                if (n[t] == 0) continue;
+                if (!mbar_wait(bar(kBarQFull + t), 0, abort_flag)) {
+                    report_timeout(p.status, 1, 8, 0, 300 + t);
+                    ok = false;
+                    break;
+                }
+                const bool reuse = shared_mode && t == 1;
+                slot_k[t] = reuse ? slot_k[0] : acquire(310 + t);
+                if (!ok) break;
+                tc_fence_after();
+                mma_tile_kk(tS[t], sQ[t], ring(slot_k[t]), false);
+                umma_commit(bar(kBarSFull + t));
+                if (!shared_mode || t == 1) umma_commit(bar(kBarRingEmpty + slot_k[t]));
+            }
+            const int nmax = n[0] > n[1] ? n[0] : n[1];
+            for (int i = 0; i < nmax && ok; ++i) {
+                for (int t = 0; t < 2 && ok; ++t) {
+                    if (i >= n[t]) continue;
+                    const bool reuse = shared_mode && t == 1;
+                    const bool release = !shared_mode || t == 1;
+                    if (!mbar_wait(bar(kBarPReady + t), i & 1u, abort_flag)) {
+                        report_timeout(p.status, 1, 8, i, 320 + t);
+                        ok = false;
+                        break;
+                    }
+                    slot_v[t] = reuse ? slot_v[0] : acquire(330 + t);
+                    if (!ok) break;
+                    tc_fence_after();
+                    mma_tile_tm(tO[t], tS[t], tS[t] + 32, ring(slot_v[t]), i > 0);
+                    if (release) umma_commit(bar(kBarRingEmpty + slot_v[t]));
+                    if (i + 1 < n[t]) {
+                        slot_k[t] = reuse ? slot_k[0] : acquire(340 + t);
+                        if (!ok) break;
+                        tc_fence_after();
+                        mma_tile_kk(tS[t], sQ[t], ring(slot_k[t]), false);
+                        umma_commit(bar(kBarSFull + t));
+                        if (release) umma_commit(bar(kBarRingEmpty + slot_k[t]));
+                    } else {
+                        umma_commit(bar(kBarODone + t));
+                    }
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax + epilogue
+        const int t = warp >> 2;                       // 0: tile A, 1: tile B
+        const int row = (warp & 3) * 32 + lane;        // row inside the tile == TMEM lane
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t tS = tmem + lane_base + static_cast<uint32_t>(t) * 128u;
+        const uint32_t tO = tmem + lane_base + 256u + static_cast<uint32_t>(t) * 128u;
+        const bool tile_valid = mt[t] < p.n_mtiles;
+        const float c = kSoftmaxScale * kLog2e;
+        const int g = row >> 4;
+
+        float off = 0.f;        // exponent offset (scaled-by-c row max the exponentials refer to)
+        bool have_off = false;  // false until the row has seen a finite score
+        float l = 0.f;
+        bool ok = true;
+
+        for (int i = 0; i < n[t] && ok; ++i) {
+            if (!mbar_wait(bar(kBarSFull + t), i & 1u, abort_flag)) {
+                if (lane == 0) report_timeout(p.status, 1, static_cast<uint32_t>(warp), i, 400 + t);
+                ok = false;
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t u[128];
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc)
+                tmem_ld32(tS + 32u * cc, reinterpret_cast<uint32_t(&)[32]>(u[32 * cc]));
+            tmem_wait_ld();
+
+            if (p.list.msk != nullptr) {
+                const uint32_t w = p.list.msk[lrow[t] * p.list.stride + i / sub];
+                if (w != 0xffffu) {
+                    const bool keep0 = (w >> g) & 1u, keep1 = (w >> (8 + g)) & 1u;
+#pragma unroll
+                    for (int j = 0; j < 64; ++j) {
+                        if (!keep0) u[j] = 0xff800000u;
+                        if (!keep1) u[64 + j] = 0xff800000u;
+                    }
+                }
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 128; ++j) mx = fmaxf(mx, __uint_as_float(u[j]));
+
+            float alpha = 1.f;
+            const float cand = mx * c;
+            if (!have_off) {
+                if (mx > -INFINITY) {
+                    off = cand;
+                    have_off = true;
+                }
+            } else if (cand - off > 8.f) {
+                alpha = ex2_approx(off - cand);
+                off = cand;
+            }
+            if (i > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                // Rescale this warp's 32 rows of O.  The previous P V of this tile has completed
+                // (the commit that released S covers it) and the next one waits for p_ready.
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                    uint32_t v[32];
+                    tmem_ld32(tO + 32u * cc, v);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+                    tmem_st32(tO + 32u * cc, v);
+                }
+            }
+            l *= alpha;
+            const float neg_off = have_off ? -off : 0.f;
+#pragma unroll
+            for (int cc = 0; cc < 8; ++cc) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float p0 = ex2_approx(fmaf(__uint_as_float(u[16 * cc + 2 * j]), c, neg_off));
+                    const float p1 = ex2_approx(fmaf(__uint_as_float(u[16 * cc + 2 * j + 1]), c, neg_off));
+                    l += p0 + p1;
+                    pk[j] = pack_bf16x2(p0, p1);
+                }
+                // 16 scores -> 8 packed columns
+                asm volatile(
+                    "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(
+                        tS + 8u * cc),
+                    "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]), "r"(pk[6]),
+                    "r"(pk[7])
+                    : "memory");
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(kBarPReady + t));
+        }
+
+        // Epilogue: O / l -> bf16 -> swizzled staging in this tile's Q buffer -> TMA store.
+        if (tile_valid) {
+            if (n[t] > 0 && ok) {
+                if (!mbar_wait(bar(kBarODone + t), 0, abort_flag)) {
+                    if (lane == 0) report_timeout(p.status, 1, static_cast<uint32_t>(warp), 0, 500 + t);
+                    ok = false;
+                }
+                ok = __all_sync(0xffffffffu, ok);
+            }
+            if (ok) {
+                tc_fence_after();
+                const float inv_l = l > 0.f ? 1.f / l : 0.f;
+                uint8_t* stage = base_ptr + kFwdSmemQ + static_cast<uint32_t>(t) * kTileBytes;
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                    uint32_t v[32];
+                    if (n[t] > 0) {
+                        tmem_ld32(tO + 32u * cc, v);
+                        tmem_wait_ld();
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = 0u;
+                    }
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 w;
+                        w.x = pack_bf16x2(__uint_as_float(v[8 * q4 + 0]) * inv_l, __uint_as_float(v[8 * q4 + 1]) * inv_l);
+                        w.y = pack_bf16x2(__uint_as_float(v[8 * q4 + 2]) * inv_l, __uint_as_float(v[8 * q4 + 3]) * inv_l);
+                        w.z = pack_bf16x2(__uint_as_float(v[8 * q4 + 4]) * inv_l, __uint_as_float(v[8 * q4 + 5]) * inv_l);
+                        w.w = pack_bf16x2(__uint_as_float(v[8 * q4 + 6]) * inv_l, __uint_as_float(v[8 * q4 + 7]) * inv_l);
+                        const int chunk = cc * 4 + q4;  // 16-byte chunk 0..15 of the 256-byte row
+                        const uint32_t o = static_cast<uint32_t>(chunk >> 3) * kPanelBytes +
+                                           static_cast<uint32_t>(row) * 128u +
+                                           (static_cast<uint32_t>((chunk & 7) ^ (row & 7)) << 4);
+                        *reinterpret_cast<uint4*>(stage + o) = w;
+                    }
+                }
+                const int grow = mt[t] * 128 + row;
+                if (grow < p.Sq)
+                    p.lse[static_cast<long long>(bh) * p.Sq + grow] =
+                        l > 0.f ? (off + lg2_approx(l)) * kLn2 : -INFINITY;
+                fence_proxy_async_smem();
+            }
+            named_bar_sync(1 + t, 128);
+            if (ok && (warp & 3) == 0 && lane == 0) {
+                tma_store_3d(&tm_o, 0, mt[t] * 128, bh, sQ[t]);
+                tma_store_3d(&tm_o, 64, mt[t] * 128, bh, sQ[t] + kPanelBytes);
+                tma_commit_group();
+                tma_wait_group0();
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+}  // namespace fba
+
+using namespace fba;
+
+static int check_list(const fba_list_t* l, const char* who) {
+    if (!l || !l->idx || !l->cnt) return set_error(FBA_ERR_BAD_ARG, who);
+    if (l->stride <= 0 || l->rows_per_bh <= 0 || l->rows_div <= 0 || l->sub <= 0 ||
+        (l->bh_stride != 0 && l->bh_stride != l->rows_per_bh))
+        return set_error(FBA_ERR_BAD_ARG, who);
+    return FBA_OK;
+}
+
+extern "C" int fba_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Hq,
+                       int Hkv, int Sq, int Skv, const fba_list_t* q2k, uint32_t* status,
+                       void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!q || !k || !v || !o || !lse || !status)
+        return set_error(FBA_ERR_BAD_ARG, "fba_fwd: null pointer argument");
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || Sq <= 0 || Skv <= 0)
+        return set_error(FBA_ERR_BAD_ARG, "fba_fwd: non-positive size");
+    if (Hq % Hkv != 0) return set_error(FBA_ERR_BAD_ARG, "fba_fwd: Hq must be a multiple of Hkv");
+    if (Sq < 128 || Skv < 128)
+        return set_error(FBA_ERR_BAD_ARG, "fba_fwd: sequence lengths below 128 are not supported");
+    int rc = check_list(q2k, "fba_fwd: malformed q2k list");
+    if (rc != FBA_OK) return rc;
+    const int n_mtiles = (Sq + 127) / 128;
+    const int n_ntiles = (Skv + 127) / 128;
+    if (static_cast<long long>(q2k->rows_per_bh) * q2k->rows_div < n_mtiles ||
+        static_cast<long long>(q2k->stride) * q2k->sub < n_ntiles)
+        return set_error(FBA_ERR_BAD_ARG, "fba_fwd: q2k list does not cover the sequences");
+    if (static_cast<long long>(B) * Hq > 65535)
+        return set_error(FBA_ERR_TOO_LARGE, "fba_fwd: B * Hq exceeds 65535");
+
+    CUtensorMap tm_q, tm_k, tm_v, tm_o;
+    if ((rc = make_tmap_bf16(&tm_q, q, Sq, static_cast<long long>(B) * Hq, 128)) != FBA_OK) return rc;
+    if ((rc = make_tmap_bf16(&tm_k, k, Skv, static_cast<long long>(B) * Hkv, 128)) != FBA_OK) return rc;
+    if ((rc = make_tmap_bf16(&tm_v, v, Skv, static_cast<long long>(B) * Hkv, 128)) != FBA_OK) return rc;
+    if ((rc = make_tmap_bf16(&tm_o, o, Sq, static_cast<long long>(B) * Hq, 128)) != FBA_OK) return rc;
+
+    {
+        cudaError_t e = cudaFuncSetAttribute(fba_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(kFwdSmemBytes));
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return set_error(FBA_ERR_LAUNCH, "fba_fwd: cannot raise the dynamic shared memory limit");
+        }
+    }
+    FwdParams p;
+    p.list = to_dev(*q2k);
+    p.lse = lse;
+    p.status = status;
+    p.n_mtiles = n_mtiles;
+    p.Sq = Sq;
+    p.Hq = Hq;
+    p.Hkv = Hkv;
+    dim3 grid((n_mtiles + 1) / 2, B * Hq);
+    fba_fwd_kernel<<<grid, kFwdThreads, kFwdSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, p);
+    return check_launch("fba_fwd_kernel");
+}

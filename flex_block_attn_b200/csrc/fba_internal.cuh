@@ -1,0 +1,28 @@
+// Host-side helpers shared by the translation units of libfba_b200.so: error reporting,
+// launch checking and TMA tensor-map construction.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/fba.h"
+
+namespace fba {
+
+// Record `msg` as the calling thread's last error and return `code`.
+int set_error(int code, const char* msg);
+// cudaGetLastError() after a launch; returns FBA_OK or FBA_ERR_LAUNCH (with text recorded).
+int check_launch(const char* what);
+
+// 3-D bf16 tensor map over a [n_bh, seq, 128] tensor viewed as (col, row, bh), box = 64 columns x
+// `box_rows` rows x 1, 128-byte swizzle, out-of-range rows read as zero and are dropped on store.
+int make_tmap_bf16(CUtensorMap* out, const void* base, int seq, long long n_bh, int box_rows);
+
+// Status-word layout written by the attention kernels when a bounded wait gives up.
+//   [0] non-zero flag   [1] kernel id (1 fwd, 2 bwd)   [2] role id   [3] blockIdx.x
+//   [4] blockIdx.y      [5] iteration                  [6] barrier tag
+struct StatusWords {
+    enum { kFlag = 0, kKernel = 1, kRole = 2, kBx = 3, kBy = 4, kIter = 5, kTag = 6, kCount = 8 };
+};
+
+}  // namespace fba

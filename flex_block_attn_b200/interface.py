@@ -1,0 +1,353 @@
+"""Python API and autograd wrapper of the B200 block-sparse attention operator.
+
+Mirrors the reference's public layer (flex_block_attn/flex_block_attn_interface.py):
+``flex_block_attn_func`` (:91-106), ``FlexBlockAttnFunc`` (:14-89) and the two pass-throughs
+``_flex_block_attn_forward`` / ``_flex_block_attn_backward`` (:6-12), with the same argument
+meaning, the same assertion texts (:18-32) and the same return convention
+(``dq, dk, dv, None x 5``, :89).  Underneath, PyTorch only allocates device buffers and supplies
+the current stream; all compute runs in libfba_b200.so through the C ABI in include/fba.h.
+
+Differences that a caller can observe:
+  * gradients come back in bf16 directly (the reference returns fp32 and lets autograd cast);
+  * the saved log-sum-exp is the natural-log one, shape [B, H, Sq, 1] (the reference stores
+    -sqrt(128) * LSE, flex_block_attn_h100.cu:303-307);
+  * the block mask is compacted once in forward into index lists that backward reuses; the
+    reference max-pools the mask (:38-66) and transposes it on every backward (:85-86);
+  * ``q_block_size > kv_block_size`` with a 2-D mask works (the reference reshapes it wrongly,
+    :55-57) and a query row that attends to nothing yields a zero output row and zero gradients.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _cabi
+from ._cabi import FbaList
+
+HEAD_DIM = 128
+TILE = 128
+
+_status_bufs: dict[int, torch.Tensor] = {}
+
+
+def _status(device: torch.device) -> torch.Tensor:
+    """Per-device 8-word status buffer the kernels write when a bounded wait gives up."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    buf = _status_bufs.get(key)
+    if buf is None:
+        buf = torch.zeros(8, dtype=torch.int32, device=device)
+        _status_bufs[key] = buf
+    return buf
+
+
+def check_status(device: Optional[torch.device] = None) -> None:
+    """Synchronise and raise if any kernel on ``device`` reported a timed-out wait."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    words = _status(device).cpu().tolist()
+    if words[0] != 0:
+        _status(device).zero_()
+        raise RuntimeError(
+            "flex_block_attn_b200: a device-side wait timed out "
+            f"(kernel={words[1]} role={words[2]} block=({words[3]},{words[4]}) iter={words[5]} tag={words[6]})"
+        )
+
+
+def _maybe_check(device: torch.device) -> None:
+    if os.environ.get("FBA_CHECK_STATUS", "0") == "1":
+        check_status(device)
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+@dataclass
+class SparseLists:
+    """Compacted index lists of one block mask, in the layout the kernels walk.
+
+    ``q2k_*`` / ``k2q_*`` are the block-granular lists (always built when both block sizes are
+    multiples of 128; they are then exactly what the kernels consume).  For other block sizes the
+    kernels consume 128x128 tile lists with 16-bit sub-tile masks (``fwd_*`` / ``bwd_*``).
+    """
+
+    aligned: bool
+    mask_dim: int
+    B: int
+    H: int
+    nQ: int
+    nK: int
+    q_block: int
+    kv_block: int
+    Sq: int
+    Skv: int
+    fwd_idx: torch.Tensor
+    fwd_cnt: torch.Tensor
+    fwd_msk: Optional[torch.Tensor]
+    bwd_idx: Optional[torch.Tensor]
+    bwd_cnt: Optional[torch.Tensor]
+    bwd_msk: Optional[torch.Tensor]
+
+    def fwd_list(self) -> FbaList:
+        n_mt = (self.Sq + TILE - 1) // TILE
+        rows = self.nQ if self.aligned else n_mt
+        return FbaList(
+            self.fwd_idx.data_ptr(), self.fwd_cnt.data_ptr(), _ptr(self.fwd_msk),
+            self.fwd_idx.shape[-1], rows, rows if self.mask_dim == 4 else 0,
+            self.q_block // TILE if self.aligned else 1,
+            self.kv_block // TILE if self.aligned else 1,
+        )
+
+    def bwd_list(self) -> FbaList:
+        assert self.bwd_idx is not None and self.bwd_cnt is not None
+        n_nt = (self.Skv + TILE - 1) // TILE
+        rows = self.nK if self.aligned else n_nt
+        return FbaList(
+            self.bwd_idx.data_ptr(), self.bwd_cnt.data_ptr(), _ptr(self.bwd_msk),
+            self.bwd_idx.shape[-1], rows, rows if self.mask_dim == 4 else 0,
+            self.kv_block // TILE if self.aligned else 1,
+            self.q_block // TILE if self.aligned else 1,
+        )
+
+
+def build_index(block_mask: torch.Tensor, want_q2k: bool = True, want_k2q: bool = True):
+    """Block-granular compaction: returns (q2k_idx, q2k_cnt, k2q_idx, k2q_cnt), int32.
+
+    ``q2k_idx[r, :q2k_cnt[r]]`` are the ascending kv-block indices q-block row r attends to (rows
+    are flattened over batch and head for a 4-D mask); unused slots are -1.  ``k2q_*`` is the same
+    for the transposed mask.  Bit-exact against a ``torch.nonzero`` restatement.
+    """
+    if block_mask.dtype != torch.bool:
+        raise TypeError("block_mask must be a torch.bool tensor")
+    if not block_mask.is_cuda:
+        raise RuntimeError("block_mask must be a CUDA tensor (there is no CPU path)")
+    if block_mask.dim() not in (2, 4):
+        raise ValueError("block_mask must have 2 or 4 dimensions")
+    m = block_mask.contiguous()
+    dev = m.device
+    if m.dim() == 2:
+        B = H = 1
+        nQ, nK = m.shape
+    else:
+        B, H, nQ, nK = m.shape
+    n_bh = B * H if m.dim() == 4 else 1
+    q2k_idx = q2k_cnt = k2q_idx = k2q_cnt = None
+    if want_q2k:
+        q2k_idx = torch.empty((n_bh * nQ, nK), dtype=torch.int32, device=dev)
+        q2k_cnt = torch.empty((n_bh * nQ,), dtype=torch.int32, device=dev)
+    if want_k2q:
+        k2q_idx = torch.empty((n_bh * nK, nQ), dtype=torch.int32, device=dev)
+        k2q_cnt = torch.empty((n_bh * nK,), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _cabi.lib().fba_build_index(
+            m.data_ptr(), m.dim(), B, H, nQ, nK, _ptr(q2k_idx), _ptr(q2k_cnt), _ptr(k2q_idx),
+            _ptr(k2q_cnt), _stream_ptr(dev))
+    _cabi.check(rc, "fba_build_index")
+    return q2k_idx, q2k_cnt, k2q_idx, k2q_cnt
+
+
+def build_lists(block_mask: torch.Tensor, q_block: int, kv_block: int, Sq: int, Skv: int,
+                need_bwd: bool = True) -> SparseLists:
+    """Compact ``block_mask`` into the lists the forward (and backward) kernels walk."""
+    if block_mask.dtype != torch.bool:
+        raise TypeError("block_mask must be a torch.bool tensor")
+    if not block_mask.is_cuda:
+        raise RuntimeError("block_mask must be a CUDA tensor (there is no CPU path)")
+    m = block_mask.contiguous()
+    dev = m.device
+    if m.dim() == 2:
+        B = H = 1
+        nQ, nK = m.shape
+    else:
+        B, H, nQ, nK = m.shape
+    aligned = q_block % TILE == 0 and kv_block % TILE == 0
+    if aligned:
+        q2k_idx, q2k_cnt, k2q_idx, k2q_cnt = build_index(m, True, need_bwd)
+        return SparseLists(aligned, m.dim(), B, H, nQ, nK, q_block, kv_block, Sq, Skv,
+                           q2k_idx, q2k_cnt, None, k2q_idx, k2q_cnt, None)
+    n_bh = B * H if m.dim() == 4 else 1
+    n_mt = (Sq + TILE - 1) // TILE
+    n_nt = (Skv + TILE - 1) // TILE
+    fwd_idx = torch.empty((n_bh * n_mt, n_nt), dtype=torch.int32, device=dev)
+    fwd_cnt = torch.empty((n_bh * n_mt,), dtype=torch.int32, device=dev)
+    fwd_msk = torch.empty((n_bh * n_mt, n_nt), dtype=torch.int16, device=dev)
+    bwd_idx = bwd_cnt = bwd_msk = None
+    if need_bwd:
+        bwd_idx = torch.empty((n_bh * n_nt, n_mt), dtype=torch.int32, device=dev)
+        bwd_cnt = torch.empty((n_bh * n_nt,), dtype=torch.int32, device=dev)
+        bwd_msk = torch.empty((n_bh * n_nt, n_mt), dtype=torch.int16, device=dev)
+    with torch.cuda.device(dev):
+        rc = _cabi.lib().fba_build_tile_lists(
+            m.data_ptr(), m.dim(), B, H, nQ, nK, q_block, kv_block, Sq, Skv,
+            fwd_idx.data_ptr(), fwd_cnt.data_ptr(), fwd_msk.data_ptr(),
+            _ptr(bwd_idx), _ptr(bwd_cnt), _ptr(bwd_msk), _stream_ptr(dev))
+    _cabi.check(rc, "fba_build_tile_lists")
+    return SparseLists(aligned, m.dim(), B, H, nQ, nK, q_block, kv_block, Sq, Skv,
+                       fwd_idx, fwd_cnt, fwd_msk, bwd_idx, bwd_cnt, bwd_msk)
+
+
+def _check_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        if not t.is_cuda:
+            raise RuntimeError(f"{name} must be a CUDA tensor (there is no CPU path)")
+        if t.dtype != torch.bfloat16:
+            raise TypeError(f"{name} must be torch.bfloat16")
+        if t.dim() != 4:
+            raise ValueError(f"{name} must have shape [batch, heads, seq, head_dim]")
+        if not t.is_contiguous():
+            raise RuntimeError(f"{name} must be contiguous")
+    if q.shape[-1] != HEAD_DIM or k.shape[-1] != HEAD_DIM or v.shape[-1] != HEAD_DIM:
+        raise ValueError("head_dim must be 128")
+    if k.shape != v.shape:
+        raise ValueError("k and v must have the same shape")
+    if q.shape[0] != k.shape[0]:
+        raise ValueError("q and k must have the same batch size")
+    if q.shape[1] % k.shape[1] != 0:
+        raise ValueError("the number of query heads must be a multiple of the number of kv heads")
+    if q.device != k.device or q.device != v.device:
+        raise RuntimeError("q, k and v must be on the same device")
+
+
+def forward_with_lists(q, k, v, lists: SparseLists):
+    """Run the forward kernel; returns (o bf16 [B,H,Sq,128], lse fp32 [B,H,Sq])."""
+    _check_qkv(q, k, v)
+    B, Hq, Sq, _ = q.shape
+    Hkv, Skv = k.shape[1], k.shape[2]
+    dev = q.device
+    o = torch.empty_like(q)
+    lse = torch.empty((B, Hq, Sq), dtype=torch.float32, device=dev)
+    lst = lists.fwd_list()
+    with torch.cuda.device(dev):
+        rc = _cabi.lib().fba_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                 B, Hq, Hkv, Sq, Skv, ctypes.byref(lst), _status(dev).data_ptr(),
+                                 _stream_ptr(dev))
+    _cabi.check(rc, "fba_fwd")
+    _maybe_check(dev)
+    return o, lse
+
+
+def backward_with_lists(q, k, v, o, lse, dout, lists: SparseLists):
+    """Run the backward kernels; returns (dq, dk, dv) in bf16."""
+    _check_qkv(q, k, v)
+    B, Hq, Sq, _ = q.shape
+    Hkv, Skv = k.shape[1], k.shape[2]
+    dev = q.device
+    if dout.dtype != torch.bfloat16:
+        dout = dout.to(torch.bfloat16)
+    dout = dout.contiguous()
+    o = o.contiguous()
+    lse = lse.reshape(B, Hq, Sq).contiguous()
+    if lse.dtype != torch.float32:
+        raise TypeError("lse must be torch.float32")
+    dq = torch.empty_like(q)
+    dk = torch.empty_like(k)
+    dv = torch.empty_like(v)
+    n1, n2 = ctypes.c_uint64(0), ctypes.c_uint64(0)
+    _cabi.check(_cabi.lib().fba_bwd_scratch_bytes(B, Hq, Sq, ctypes.byref(n1), ctypes.byref(n2)),
+                "fba_bwd_scratch_bytes")
+    lse_delta = torch.empty((n1.value // 4,), dtype=torch.float32, device=dev)
+    dq_accum = torch.empty((n2.value // 4,), dtype=torch.float32, device=dev)
+    lst = lists.bwd_list()
+    with torch.cuda.device(dev):
+        rc = _cabi.lib().fba_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                 dout.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                 B, Hq, Hkv, Sq, Skv, ctypes.byref(lst), lse_delta.data_ptr(),
+                                 dq_accum.data_ptr(), _status(dev).data_ptr(), _stream_ptr(dev))
+    _cabi.check(rc, "fba_bwd")
+    _maybe_check(dev)
+    return dq, dk, dv
+
+
+def _fine_mask(block_mask, small_block_mask, use_small_block_mode):
+    return small_block_mask if (use_small_block_mode and small_block_mask is not None) else block_mask
+
+
+def _flex_block_attn_forward(q, k, v, q_block_size, kv_block_size, block_mask, small_block_mask=None,
+                             use_small_block_mode=False):
+    """Same call shape as the reference pass-through (interface.py:6-8); returns (o, lse).
+
+    ``small_block_mask`` is the mask at [Sq/q_block, Skv/kv_block] granularity and is the one used
+    when ``use_small_block_mode`` is set (``block_mask`` is then the pooled mask, which this
+    implementation does not need).  ``lse`` is fp32 [B, H, Sq, 1], natural log.
+    """
+    mask = _fine_mask(block_mask, small_block_mask, use_small_block_mode)
+    lists = build_lists(mask, q_block_size, kv_block_size, q.shape[2], k.shape[2], need_bwd=False)
+    o, lse = forward_with_lists(q, k, v, lists)
+    return o, lse.unsqueeze(-1)
+
+
+def _flex_block_attn_backward(q, k, v, o, lse, do, q_block_size, kv_block_size, block_mask,
+                              small_block_mask=None, use_small_block_mode=False):
+    """Same call shape as the reference pass-through (interface.py:10-12); returns (dq, dk, dv).
+
+    Like the reference's, the masks arrive TRANSPOSED ([.., Skv/kv_block, Sq/q_block], reference
+    interface.py:85-86).
+    """
+    mask_t = _fine_mask(block_mask, small_block_mask, use_small_block_mode)
+    mask = mask_t.transpose(-1, -2).contiguous()
+    lists = build_lists(mask, q_block_size, kv_block_size, q.shape[2], k.shape[2], need_bwd=True)
+    return backward_with_lists(q, k, v, o, lse, do, lists)
+
+
+class FlexBlockAttnFunc(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, q_block_size, kv_block_size, block_mask, is_grad_enabled):
+        assert q_block_size % 16 == 0, f"q_block_size ({q_block_size}) must be divisible by 16"
+        assert kv_block_size % 64 == 0, f"kv_block_size ({kv_block_size}) must be divisible by 64"
+        assert kv_block_size % q_block_size == 0 or q_block_size % kv_block_size == 0, \
+            f"kv_block_size ({kv_block_size}) must be divisible by q_block_size ({q_block_size}), or vice versa."
+        _, _, q_seq_len, _ = q.shape
+        _, _, kv_seq_len, _ = k.shape
+        assert q_seq_len % q_block_size == 0, \
+            f"q_seq_len ({q_seq_len}) must be divisible by q_block_size ({q_block_size})"
+        assert kv_seq_len % kv_block_size == 0, \
+            f"kv_seq_len ({kv_seq_len}) must be divisible by kv_block_size ({kv_block_size})"
+        if block_mask.dim() == 2:
+            q_block_num, kv_block_num = block_mask.shape
+        else:
+            _, _, q_block_num, kv_block_num = block_mask.shape
+            assert block_mask.shape[0] == q.shape[0] and block_mask.shape[1] == q.shape[1], \
+                "a 4-D block_mask must have the batch and head sizes of q"
+        assert q_block_size * q_block_num == q_seq_len, \
+            f"q_block_size ({q_block_size}) * q_block_num ({q_block_num}) must equal q_seq_len ({q_seq_len}"
+        assert kv_block_size * kv_block_num == kv_seq_len, \
+            f"kv_block_size ({kv_block_size}) * kv_block_num ({kv_block_num}) must equal kv_seq_len ({kv_seq_len}"
+
+        is_grad = is_grad_enabled and any(x.requires_grad for x in [q, k, v])
+        lists = build_lists(block_mask, q_block_size, kv_block_size, q_seq_len, kv_seq_len, need_bwd=is_grad)
+        o, lse = forward_with_lists(q, k, v, lists)
+        if is_grad:
+            ctx.save_for_backward(q, k, v, o, lse)
+            ctx.lists = lists
+        return o
+
+    @staticmethod
+    def backward(ctx, dout, *args):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = backward_with_lists(q, k, v, o, lse, dout, ctx.lists)
+        return dq, dk, dv, None, None, None, None
+
+
+def flex_block_attn_func(q, k, v, q_block_size, kv_block_size, block_mask):
+    """Block-sparse attention, drop-in for the reference's function of the same name.
+
+    Args:
+        q: [batch, heads, q_seq_len, 128] bf16 CUDA tensor
+        k, v: [batch, kv_heads, kv_seq_len, 128] bf16 CUDA tensors (heads % kv_heads == 0)
+        q_block_size: query block size (multiple of 16)
+        kv_block_size: key/value block size (multiple of 64; one block size divides the other)
+        block_mask: bool [q_seq_len/q_block_size, kv_seq_len/kv_block_size] or
+            [batch, heads, ...same...]; True = the query block attends to the key block
+
+    Returns:
+        [batch, heads, q_seq_len, 128] bf16; differentiable w.r.t. q, k and v.
+    """
+    return FlexBlockAttnFunc.apply(q, k, v, q_block_size, kv_block_size, block_mask, torch.is_grad_enabled())

@@ -1,0 +1,121 @@
+/*
+ * C ABI of the B200 (sm_100a) block-sparse attention library, libfba_b200.so.
+ *
+ * This is the boundary the Python autograd layer binds with ctypes.  It stands where the reference
+ * project's pybind module `flex_block_attn_cuda` stood (reference attn.cpp:24-32, which exports
+ * attn_forward / attn_backward and forwards to attention_forward / attention_backward in
+ * flex_block_attn/flex_block_attn_h100.cu:810 and :1009).  Differences from that boundary, all
+ * deliberate:
+ *   - plain pointers and sizes only; the caller owns every buffer (no hidden allocation);
+ *   - the work is stream-ordered on the stream passed in, with no device-wide synchronisation
+ *     (the reference synchronises the device around every launch, .cu:882, 1004, 1113, 1212, 1263);
+ *   - errors are integer status codes, never C++ exceptions; fba_last_error() gives the text;
+ *   - the bool block mask is first compacted into index lists (fba_build_index /
+ *     fba_build_tile_lists) which the attention kernels walk, instead of being scanned inside
+ *     the attention kernels (reference .cu:107-121, 131-149, 642-699).
+ *
+ * Tensor layouts (all contiguous, device memory):
+ *   q, o, dout, dq : bf16 [B, Hq,  Sq,  128]
+ *   k, v, dk, dv   : bf16 [B, Hkv, Skv, 128]      Hq % Hkv == 0, head h reads kv head h / (Hq/Hkv)
+ *   lse            : fp32 [B, Hq, Sq]   natural-log sum-exp of the scaled scores of each row
+ *                    (-inf for a row that attends to nothing; its output row is 0)
+ *   block mask     : uint8 (bool) [nQ, nK] (mask_dim 2, shared by every batch and head) or
+ *                    [B, Hq, nQ, nK] (mask_dim 4); non-zero = attend
+ * The softmax scale is fixed at 1/sqrt(128) (reference .cu:177) and head_dim at 128 (.cu:833).
+ *
+ * List format ("list" = fba_list_t): for list row r, entries idx[r * stride + e], e < cnt[r], are
+ * ascending; unused slots hold -1.  `rows_per_bh` is the number of list rows of one (batch, head);
+ * `bh_stride` is rows_per_bh for a per-head list and 0 for a list shared by all heads.
+ * `rows_div` consecutive 128-row tiles share one list row and every entry stands for `sub`
+ * consecutive 128-row tiles of the other sequence; `msk` (nullable) carries one 16-bit word per
+ * entry: bit (8 * h + g) says whether 16-row query group g (0..7) of the 128-row query tile
+ * attends to 64-row half h (0..1) of the 128-row key tile.
+ */
+#ifndef FBA_H_
+#define FBA_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FBA_ABI_VERSION 1
+#define FBA_HEAD_DIM 128
+#define FBA_TILE 128
+
+/* Status codes (0 = success; negative = error). */
+#define FBA_OK 0
+#define FBA_ERR_BAD_ARG (-1)        /* null pointer, bad size, unsupported block size ... */
+#define FBA_ERR_LAUNCH (-2)         /* CUDA reported an error at or before the launch */
+#define FBA_ERR_DRIVER (-3)         /* could not resolve / run cuTensorMapEncodeTiled */
+#define FBA_ERR_TIMEOUT (-4)        /* a bounded device-side wait gave up (see status words) */
+#define FBA_ERR_TOO_LARGE (-5)      /* problem exceeds a documented fixed limit */
+
+typedef struct fba_list {
+    const int32_t* idx;   /* [rows_total, stride] */
+    const int32_t* cnt;   /* [rows_total] */
+    const uint16_t* msk;  /* [rows_total, stride] or NULL (every entry fully dense) */
+    int32_t stride;       /* entries per list row */
+    int32_t rows_per_bh;  /* list rows belonging to one (batch, head) */
+    int32_t bh_stride;    /* rows_per_bh, or 0 when one list serves every (batch, head) */
+    int32_t rows_div;     /* 128-row tiles per list row */
+    int32_t sub;          /* 128-row tiles per entry */
+} fba_list_t;
+
+int fba_abi_version(void);
+/* Text of the most recent error on the calling thread ("" if none). */
+const char* fba_last_error(void);
+
+/*
+ * Block-mask -> index-list compaction (integer work, bit-exact against a nonzero()-based
+ * restatement).  Replaces the per-call mask pooling and transposes of the reference's Python layer
+ * (flex_block_attn/flex_block_attn_interface.py:38-66, 85-86) and the in-kernel mask scans.
+ *   q2k_idx int32 [R, nK], q2k_cnt int32 [R]    R  = nQ (mask_dim 2) or B*H*nQ (mask_dim 4)
+ *   k2q_idx int32 [Rk, nQ], k2q_cnt int32 [Rk]  Rk = nK (mask_dim 2) or B*H*nK
+ * Either pair may be NULL to skip that direction.
+ */
+int fba_build_index(const uint8_t* mask, int mask_dim, int B, int H, int nQ, int nK,
+                    int32_t* q2k_idx, int32_t* q2k_cnt, int32_t* k2q_idx, int32_t* k2q_cnt,
+                    void* stream);
+
+/*
+ * 128x128-tile lists with 16-bit sub-tile masks, for block sizes that are not multiples of 128
+ * (any q_block % 16 == 0, kv_block % 64 == 0).  nMt = ceil(Sq/128), nNt = ceil(Skv/128).
+ *   fwd_idx int32 [R, nNt], fwd_cnt int32 [R], fwd_msk uint16 [R, nNt]   R  = nMt or B*H*nMt
+ *   bwd_idx int32 [Rk, nMt], bwd_cnt int32 [Rk], bwd_msk uint16 [Rk, nMt] Rk = nNt or B*H*nNt
+ * Either triple may be NULL.
+ */
+int fba_build_tile_lists(const uint8_t* mask, int mask_dim, int B, int H, int nQ, int nK,
+                         int q_block, int kv_block, int Sq, int Skv, int32_t* fwd_idx,
+                         int32_t* fwd_cnt, uint16_t* fwd_msk, int32_t* bwd_idx, int32_t* bwd_cnt,
+                         uint16_t* bwd_msk, void* stream);
+
+/*
+ * Forward (replaces attention_forward, reference .cu:810-1007, and fwd_attend_ker, .cu:52-318).
+ * `q2k` is the query-major list.  `status` points at 8 zero-initialised uint32 words in device
+ * memory; word 0 becomes non-zero if a bounded wait inside the kernel gave up (then the outputs
+ * are undefined), words 1.. say where.
+ */
+int fba_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Hq,
+            int Hkv, int Sq, int Skv, const fba_list_t* q2k, uint32_t* status, void* stream);
+
+/*
+ * Backward (replaces attention_backward, reference .cu:1009-1267, bwd_attend_prep_ker .cu:339-389
+ * and bwd_attend_ker .cu:572-802).  Gradients come back in bf16.
+ *   k2q      : key-major list (entries are query tiles)
+ *   lse_delta: scratch fp32 [B*Hq, nMt*128, 2]   (nMt = ceil(Sq/128))
+ *   dq_accum : scratch fp32 [B*Hq, nMt*128, 128]; zeroed by this call
+ * Both scratch buffers are caller-allocated; fba_bwd_scratch_bytes() gives their sizes.
+ */
+int fba_bwd_scratch_bytes(int B, int Hq, int Sq, uint64_t* lse_delta_bytes,
+                          uint64_t* dq_accum_bytes);
+int fba_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse,
+            const void* dout, void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int Sq,
+            int Skv, const fba_list_t* k2q, float* lse_delta, float* dq_accum, uint32_t* status,
+            void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FBA_H_ */

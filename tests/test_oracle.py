@@ -1,0 +1,95 @@
+"""CPU tests that pin the oracle: against the golden vectors produced by the reference's own
+oracle code, and against itself (explicit == slab == SDPA; integer list restatements)."""
+import pytest
+import torch
+
+from oracle import dense_oracle as orc
+from tests.util import GOLDEN_CASES, bernoulli_mask, load_golden, rand_qkv, reference_rule_mask
+
+
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_explicit_matches_reference_golden(name):
+    g = load_golden(name)
+    o, lse, dq, dk, dv = orc.attention_explicit(g["q"], g["k"], g["v"], g["block_mask"], g["q_block"],
+                                                g["kv_block"], g["do"])
+    scale = max(1.0, g["o"].abs().max().item())
+    for got, want, nm in ((o, g["o"], "o"), (dq, g["dq"], "dq"), (dk, g["dk"], "dk"), (dv, g["dv"], "dv")):
+        tol = 2e-5 * max(1.0, want.abs().max().item())
+        assert torch.allclose(got, want, rtol=1e-4, atol=tol), (name, nm, (got - want).abs().max().item(), scale)
+
+
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_slab_matches_reference_golden(name):
+    g = load_golden(name)
+    o, lse, dq, dk, dv = orc.attention_slab(g["q"], g["k"], g["v"], g["block_mask"], g["q_block"],
+                                            g["kv_block"], g["do"])
+    for got, want, nm in ((o, g["o"], "o"), (dq, g["dq"], "dq"), (dk, g["dk"], "dk"), (dv, g["dv"], "dv")):
+        tol = 2e-5 * max(1.0, want.abs().max().item())
+        assert torch.allclose(got, want, rtol=1e-4, atol=tol), (name, nm)
+
+
+def test_config1_explicit_slab_sdpa_agree():
+    """BASELINE config 1: B=1, H=2, S=1536, D=128, 384-blocks, Bernoulli(0.5)|diag mask, fp32."""
+    q, k, v, do = rand_qkv(1, 2, 2, 1536, 1536, seed=0, dtype=torch.float32)
+    mask = bernoulli_mask((4, 4), 0.5, seed=0)
+    qr, kr, vr = (t.clone().requires_grad_() for t in (q, k, v))
+    o_ref = orc.sdpa_dense(qr, kr, vr, mask, 384, 384)
+    o_ref.backward(do)
+    for fn in (orc.attention_explicit, orc.attention_slab):
+        o, lse, dq, dk, dv = fn(q, k, v, mask, 384, 384, do)
+        assert torch.allclose(o, o_ref, atol=1e-5, rtol=1e-4)
+        assert torch.allclose(dq, qr.grad, atol=2e-5, rtol=1e-4)
+        assert torch.allclose(dk, kr.grad, atol=2e-5, rtol=1e-4)
+        assert torch.allclose(dv, vr.grad, atol=2e-5, rtol=1e-4)
+
+
+def test_gqa_4d_mask_and_asymmetric_blocks():
+    q, k, v, do = rand_qkv(2, 4, 2, 256, 384, seed=3, dtype=torch.float32)
+    mask = bernoulli_mask((2, 4, 256 // 32, 384 // 128), 0.5, seed=4)
+    a = orc.attention_explicit(q, k, v, mask, 32, 128, do)
+    b = orc.attention_slab(q, k, v, mask, 32, 128, do)
+    for x, y in zip(a, b):
+        assert torch.allclose(x, y, atol=2e-5, rtol=1e-4)
+    qr, kr, vr = (t.clone().requires_grad_() for t in (q, k, v))
+    o_ref = orc.sdpa_dense(qr, kr, vr, mask, 32, 128)
+    o_ref.backward(do)
+    assert torch.allclose(a[0], o_ref, atol=1e-5, rtol=1e-4)
+    assert torch.allclose(a[3], kr.grad, atol=2e-5, rtol=1e-4)
+
+
+def test_dead_rows_are_zero():
+    q, k, v, do = rand_qkv(1, 1, 1, 256, 256, seed=5, dtype=torch.float32)
+    mask = torch.tensor([[True, False], [False, False]])
+    o, lse, dq, dk, dv = orc.attention_explicit(q, k, v, mask, 128, 128, do)
+    assert (o[:, :, 128:] == 0).all() and torch.isinf(lse[:, :, 128:]).all()
+    assert (dq[:, :, 128:] == 0).all() and (dk[:, :, 128:] == 0).all()
+    assert torch.isfinite(dq).all() and torch.isfinite(dk).all() and torch.isfinite(dv).all()
+
+
+def test_index_lists_by_hand():
+    m = torch.tensor([[1, 0, 1, 1], [0, 0, 0, 0], [0, 1, 0, 0]], dtype=torch.bool)
+    q2k_idx, q2k_cnt, k2q_idx, k2q_cnt = orc.block_index_oracle(m)
+    assert q2k_idx.tolist() == [[0, 2, 3, -1], [-1, -1, -1, -1], [1, -1, -1, -1]]
+    assert q2k_cnt.tolist() == [3, 0, 1]
+    assert k2q_idx.tolist() == [[0, -1, -1], [2, -1, -1], [0, -1, -1], [0, -1, -1]]
+    assert k2q_cnt.tolist() == [1, 1, 1, 1]
+
+
+def test_tile_words_by_loops():
+    q_block, kv_block, Sq, Skv = 48, 192, 48 * 7, 192 * 2
+    m = reference_rule_mask(7, 2)
+    w = orc.tile_mask_words(m, q_block, kv_block, Sq, Skv)
+    n_mt, n_nt = (Sq + 127) // 128, (Skv + 127) // 128
+    assert tuple(w.shape) == (n_mt, n_nt)
+    for mt in range(n_mt):
+        for nt in range(n_nt):
+            exp = 0
+            for h in range(2):
+                for g in range(8):
+                    r, c = mt * 128 + g * 16, nt * 128 + h * 64
+                    if r < Sq and c < Skv and m[r // q_block, c // kv_block]:
+                        exp |= 1 << (8 * h + g)
+            assert int(w[mt, nt]) == exp
+    fi, fc, fm, bi, bc, bm = orc.tile_lists_oracle(m, q_block, kv_block, Sq, Skv)
+    assert fi.shape == (n_mt, n_nt) and bi.shape == (n_nt, n_mt)
+    assert int(fc.sum()) == int(bc.sum()) == int((w != 0).sum())
