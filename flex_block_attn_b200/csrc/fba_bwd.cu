@@ -1,6 +1,504 @@
+// Block-sparse attention backward for sm_100a.
+//
+// Three kernels, in stream order:
+//   1. bwd_prep_kernel      (lse2, delta)[row] = (LSE * log2 e, sum_d dO * O); the counterpart of
+//                           the reference's bwd_attend_prep_ker (flex_block_attn_h100.cu:339-389).
+//                           HBM-bound, one pass over O and dO.
+//   2. fba_bwd_kernel       key-major main kernel, the counterpart of bwd_attend_ker (.cu:572-802).
+//                           A CTA owns one 128-row K/V tile and walks the key-major list of query
+//                           tiles.  Per query tile, five 128x128x128 tcgen05 GEMMs:
+//                             S^T  = K Q^T          (smem x smem -> TMEM)
+//                             dP^T = V dO^T         (smem x smem -> TMEM)
+//                             dV  += P^T dO         (P^T bf16 in TMEM x smem)
+//                             dK  += dS^T Q         (dS^T bf16 in smem x smem)
+//                             dQ   = dS K           (smem x smem -> TMEM, then fp32 red.add to HBM)
+//                           TMEM columns: [0,128) S^T / P^T, [128,256) dV, [256,384) dP^T then dQ,
+//                           [384,512) dK.  dK and dV stay in TMEM for the whole CTA (and across
+//                           the query heads of a grouped-query group), so they are written once,
+//                           in bf16, with no atomics; the reference reduce-adds fp32 tiles
+//                           (.cu:544-570) into zero-filled buffers (.cu:1077-1088).
+//   3. bwd_dq_convert_kernel  dQ fp32 accumulator (tile-blocked layout) -> bf16 [B,H,Sq,128].
+//
+// Warp roles of the main kernel (448 threads): warps 0-7 compute P^T and dS^T (thread = key row;
+// warps 0-3 take query columns 0-63 of the tile, warps 4-7 columns 64-127), warps 8-11 drain dQ
+// from TMEM and issue the vector reductions, warp 12 issues every MMA, warp 13 drives TMA.
 #include "fba_common.cuh"
+
+namespace fba {
+
+constexpr int kBwdThreads = 448;
+constexpr uint32_t kBwdSmemK = 0;
+constexpr uint32_t kBwdSmemV = 1 * kTileBytes;
+constexpr uint32_t kBwdSmemQ = 2 * kTileBytes;    // 2 stages
+constexpr uint32_t kBwdSmemDO = 4 * kTileBytes;   // 2 stages
+constexpr uint32_t kBwdSmemDS = 6 * kTileBytes;
+constexpr uint32_t kBwdSmemLD = 7 * kTileBytes;   // 2 stages x 128 x (lse2, delta)
+constexpr uint32_t kBwdSmemBars = kBwdSmemLD + 2 * 1024;
+constexpr uint32_t kBwdSmemBytes = kBwdSmemBars + 128;
+
+enum BwdBar : uint32_t {
+    kBKvFull = 0,
+    kBQdoFull = 1,    // 2
+    kBQdoEmpty = 3,   // 2
+    kBSFull = 5,
+    kBPReady = 6,
+    kBDpFull = 7,
+    kBDsReady = 8,
+    kBDqFull = 9,
+    kBDqDrained = 10,
+    kBDkvDone = 11,
+    kBCount = 12
+};
+
+struct BwdParams {
+    ListDev list;          // key-major: rows = key tiles / rows_div, entries = query tiles / sub
+    const float2* ld;      // [B*Hq, nMt*128] (lse * log2e, delta)
+    float* dq_accum;       // [B*Hq, nMt, 32, 128, 4]
+    uint32_t* status;
+    int n_mtiles, Hq, Hkv;
+};
+
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) bwd_prep_kernel(const __nv_bfloat16* __restrict__ o,
+                                                      const __nv_bfloat16* __restrict__ dout,
+                                                      const float* __restrict__ lse,
+                                                      float2* __restrict__ ld, int Sq, int rows_pad,
+                                                      long long total_rows) {
+    const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    if (w >= total_rows) return;
+    const int lane = threadIdx.x & 31;
+    const long long bh = w / rows_pad;
+    const int r = static_cast<int>(w % rows_pad);
+    float2 out = make_float2(INFINITY, 0.f);
+    if (r < Sq) {
+        const long long row = bh * Sq + r;
+        const uint2 a = reinterpret_cast<const uint2*>(o + row * 128)[lane];
+        const uint2 b = reinterpret_cast<const uint2*>(dout + row * 128)[lane];
+        const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const float2 x = __bfloat1622float2(a2[j]);
+            const float2 y = __bfloat1622float2(b2[j]);
+            s = fmaf(x.x, y.x, s);
+            s = fmaf(x.y, y.y, s);
+        }
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
+        const float l = lse[row];
+        // A row that attended to nothing has LSE = -inf; +inf here makes every P of it exactly 0.
+        out = make_float2(l == -INFINITY ? INFINITY : l * kLog2e, s);
+    }
+    if (lane == 0) ld[w] = out;
+}
+
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) bwd_dq_convert_kernel(const float* __restrict__ acc,
+                                                            __nv_bfloat16* __restrict__ dq, int Sq,
+                                                            int n_mtiles) {
+    __shared__ uint2 tile[128 * 33];
+    const int mt = blockIdx.x;
+    const long long bh = blockIdx.y;
+    const float4* src = reinterpret_cast<const float4*>(acc) + (bh * n_mtiles + mt) * (32LL * 128);
+#pragma unroll 4
+    for (int k = 0; k < 16; ++k) {
+        const int i = threadIdx.x + 256 * k;  // (cg, row)
+        const int cg = i >> 7, row = i & 127;
+        const float4 v = src[i];
+        uint2 w;
+        w.x = pack_bf16x2(v.x, v.y);
+        w.y = pack_bf16x2(v.z, v.w);
+        tile[row * 33 + cg] = w;
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int k = 0; k < 8; ++k) {
+        const int i = threadIdx.x + 256 * k;  // (row, 16-byte chunk)
+        const int row = i >> 4, c = i & 15;
+        const int grow = mt * 128 + row;
+        if (grow < Sq) {
+            const uint2 a = tile[row * 33 + 2 * c], b = tile[row * 33 + 2 * c + 1];
+            uint4 w = make_uint4(a.x, a.y, b.x, b.y);
+            reinterpret_cast<uint4*>(dq + (bh * Sq + grow) * 128)[c] = w;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// D[128 x 128] (+)= A * B, A K-major in smem ([m][k]), B MN-major in smem ([k][n]).
+__device__ __forceinline__ void mma_tile_km(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem,
+                                            bool accumulate) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const uint32_t aoff = static_cast<uint32_t>(k >> 2) * kPanelBytes + static_cast<uint32_t>(k & 3) * 32u;
+        umma_ss(d_tmem, umma_desc_kmajor(a_smem + aoff), umma_desc_mnmajor(b_smem + k * 2048u), kIdescKM,
+                (accumulate || k > 0) ? 1u : 0u);
+    }
+}
+// D[128 x 128] (+)= A^T-stored * B, both MN-major in smem: A stored [k][m], B stored [k][n].
+__device__ __forceinline__ void mma_tile_mm(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem,
+                                            bool accumulate) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        umma_ss(d_tmem, umma_desc_mnmajor(a_smem + k * 2048u), umma_desc_mnmajor(b_smem + k * 2048u),
+                kIdescMM, (accumulate || k > 0) ? 1u : 0u);
+    }
+}
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c),
+                 "f"(d)
+                 : "memory");
+}
+
+__global__ void __launch_bounds__(kBwdThreads, 1)
+fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+               const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
+               const BwdParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t base = smem_u32(smem_raw);
+    uint8_t* base_ptr = smem_raw;
+    const uint32_t bars = base + kBwdSmemBars;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + kBwdSmemBars + 8 * kBCount);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + kBwdSmemBars + 8 * kBCount + 4);
+    auto bar = [&](uint32_t slot) { return bars + 8u * slot; };
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int nt = blockIdx.x;          // key tile
+    const int bhk = blockIdx.y;         // b * Hkv + kv head
+    const int hr = p.Hq / p.Hkv;
+    const int bq0 = (bhk / p.Hkv) * p.Hq + (bhk % p.Hkv) * hr;  // first query head of the group
+    const int sub = p.list.sub;
+
+    if ((base & 1023u) != 0u) {
+        // The swizzled operand panels need a 1024-byte aligned base; report instead of computing garbage.
+        if (threadIdx.x == 0) report_timeout(p.status, 2, 99, 0, 999);
+        return;
+    }
+
+    // List rows of the query heads of this group (hr is small; read on demand).
+    auto list_row = [&](int r) {
+        return static_cast<long long>(bq0 + r) * p.list.bh_stride + nt / p.list.rows_div;
+    };
+    int n_total = 0;
+    for (int r = 0; r < hr; ++r) n_total += p.list.cnt[list_row(r)] * sub;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        mbar_init(bar(kBKvFull), 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(bar(kBQdoFull + s), 1);
+            mbar_init(bar(kBQdoEmpty + s), 1);
+        }
+        mbar_init(bar(kBSFull), 1);
+        mbar_init(bar(kBPReady), 256);
+        mbar_init(bar(kBDpFull), 1);
+        mbar_init(bar(kBDsReady), 256);
+        mbar_init(bar(kBDqFull), 1);
+        mbar_init(bar(kBDqDrained), 128);
+        mbar_init(bar(kBDkvDone), 1);
+        mbar_fence_init();
+    }
+    if (warp == 12) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+        tmem_relinquish();
+    }
+    if (warp == 13 && lane == 0) {
+        tma_prefetch_desc(&tm_q);
+        tma_prefetch_desc(&tm_k);
+        tma_prefetch_desc(&tm_v);
+        tma_prefetch_desc(&tm_do);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tST = tmem + 0, tDV = tmem + 128, tDP = tmem + 256, tDK = tmem + 384;
+    const uint32_t sK = base + kBwdSmemK, sV = base + kBwdSmemV, sDS = base + kBwdSmemDS;
+    auto sQ = [&](int s) { return base + kBwdSmemQ + static_cast<uint32_t>(s) * kTileBytes; };
+    auto sDO = [&](int s) { return base + kBwdSmemDO + static_cast<uint32_t>(s) * kTileBytes; };
+
+    if (warp == 13) {
+        // ------------------------------------------------------------------ TMA loader
+        if (lane == 0 && n_total > 0) {
+            mbar_expect_tx(bar(kBKvFull), 2 * kTileBytes);
+            tma_load_3d(sK, &tm_k, 0, nt * 128, bhk, bar(kBKvFull));
+            tma_load_3d(sK + kPanelBytes, &tm_k, 64, nt * 128, bhk, bar(kBKvFull));
+            tma_load_3d(sV, &tm_v, 0, nt * 128, bhk, bar(kBKvFull));
+            tma_load_3d(sV + kPanelBytes, &tm_v, 64, nt * 128, bhk, bar(kBKvFull));
+            int it = 0;
+            bool ok = true;
+            for (int r = 0; r < hr && ok; ++r) {
+                const long long lr = list_row(r);
+                const int cnt = p.list.cnt[lr];
+                const int bq = bq0 + r;
+                for (int e = 0; e < cnt && ok; ++e) {
+                    const int q0 = p.list.idx[lr * p.list.stride + e] * sub;
+                    for (int u = 0; u < sub; ++u, ++it) {
+                        const int st = it & 1;
+                        if (!mbar_wait(bar(kBQdoEmpty + st), ((it >> 1) & 1u) ^ 1u, abort_flag)) {
+                            report_timeout(p.status, 2, 13, it, 100);
+                            ok = false;
+                            break;
+                        }
+                        const int qt = q0 + u;
+                        mbar_expect_tx(bar(kBQdoFull + st), 2 * kTileBytes + 1024);
+                        tma_load_3d(sQ(st), &tm_q, 0, qt * 128, bq, bar(kBQdoFull + st));
+                        tma_load_3d(sQ(st) + kPanelBytes, &tm_q, 64, qt * 128, bq, bar(kBQdoFull + st));
+                        tma_load_3d(sDO(st), &tm_do, 0, qt * 128, bq, bar(kBQdoFull + st));
+                        tma_load_3d(sDO(st) + kPanelBytes, &tm_do, 64, qt * 128, bq, bar(kBQdoFull + st));
+                        bulk_load(base + kBwdSmemLD + st * 1024u,
+                                  p.ld + (static_cast<long long>(bq) * p.n_mtiles + qt) * 128, 1024,
+                                  bar(kBQdoFull + st));
+                    }
+                }
+            }
+        }
+    } else if (warp == 12) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0 && n_total > 0) {
+            bool ok = true;
+            auto wait = [&](uint32_t slot, uint32_t parity, int it, uint32_t tag) {
+                if (!ok) return;
+                if (!mbar_wait(bar(slot), parity, abort_flag)) {
+                    report_timeout(p.status, 2, 12, it, tag);
+                    ok = false;
+                }
+            };
+            wait(kBKvFull, 0, 0, 200);
+            wait(kBQdoFull + 0, 0, 0, 201);
+            if (ok) {
+                tc_fence_after();
+                mma_tile_kk(tST, sK, sQ(0), false);
+                umma_commit(bar(kBSFull));
+                mma_tile_kk(tDP, sV, sDO(0), false);
+                umma_commit(bar(kBDpFull));
+            }
+            for (int it = 0; it < n_total && ok; ++it) {
+                const int st = it & 1;
+                const uint32_t ph = it & 1u;
+                wait(kBPReady, ph, it, 210);
+                if (!ok) break;
+                tc_fence_after();
+                mma_tile_tm(tDV, tST, tST + 64, sDO(st), it > 0);
+                if (it + 1 < n_total) {
+                    wait(kBQdoFull + (st ^ 1), ((it + 1) >> 1) & 1u, it, 211);
+                    if (!ok) break;
+                    tc_fence_after();
+                    mma_tile_kk(tST, sK, sQ(st ^ 1), false);
+                    umma_commit(bar(kBSFull));
+                }
+                wait(kBDsReady, ph, it, 212);
+                if (!ok) break;
+                tc_fence_after();
+                mma_tile_km(tDK, sDS, sQ(st), it > 0);
+                mma_tile_mm(tDP, sDS, sK, false);
+                umma_commit(bar(kBDqFull));
+                umma_commit(bar(kBQdoEmpty + st));
+                if (it + 1 < n_total) {
+                    wait(kBDqDrained, ph, it, 213);
+                    if (!ok) break;
+                    tc_fence_after();
+                    mma_tile_kk(tDP, sV, sDO(st ^ 1), false);
+                    umma_commit(bar(kBDpFull));
+                }
+            }
+            if (ok) umma_commit(bar(kBDkvDone));
+        }
+    } else if (warp >= 8) {
+        // ------------------------------------------------------------------ dQ drain + reduce
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;  // query row inside the tile
+        const uint32_t tdq = tDP + (static_cast<uint32_t>(quad * 32) << 16);
+        int it = 0;
+        bool ok = true;
+        for (int r = 0; r < hr && ok; ++r) {
+            const long long lr = list_row(r);
+            const int cnt = p.list.cnt[lr];
+            const long long bq = bq0 + r;
+            for (int e = 0; e < cnt && ok; ++e) {
+                const int q0 = p.list.idx[lr * p.list.stride + e] * sub;
+                for (int u = 0; u < sub && ok; ++u, ++it) {
+                    if (!mbar_wait(bar(kBDqFull), it & 1u, abort_flag)) {
+                        if (lane == 0) report_timeout(p.status, 2, static_cast<uint32_t>(warp), it, 300);
+                        ok = false;
+                    }
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    tc_fence_after();
+                    float* dst = p.dq_accum + ((bq * p.n_mtiles + (q0 + u)) * 32LL * 128 + row) * 4;
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) {
+                        uint32_t v[32];
+                        tmem_ld32(tdq + 32u * cc, v);
+                        tmem_wait_ld();
+                        if (cc == 3) {
+                            tc_fence_before();
+                            mbar_arrive(bar(kBDqDrained));
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            red_add_v4(dst + (cc * 8 + j) * 512, __uint_as_float(v[4 * j]),
+                                       __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
+                                       __uint_as_float(v[4 * j + 3]));
+                    }
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ P^T / dS^T compute
+        const int h = warp >> 2;           // query-column half of the tile
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;  // key row inside the tile == TMEM lane
+        const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+        const float c = kSoftmaxScale * kLog2e;
+        const int mbit0 = 8 * (row >> 6);  // key-half part of the mask bit index
+        int it = 0;
+        bool ok = true;
+        for (int r = 0; r < hr && ok; ++r) {
+            const long long lr = list_row(r);
+            const int cnt = p.list.cnt[lr];
+            for (int e = 0; e < cnt && ok; ++e) {
+                const uint32_t w = p.list.msk ? p.list.msk[lr * p.list.stride + e] : 0xffffu;
+                for (int u = 0; u < sub && ok; ++u, ++it) {
+                    const int st = it & 1;
+                    const float2* ld = reinterpret_cast<const float2*>(base_ptr + kBwdSmemLD + st * 1024) + 64 * h;
+                    if (!mbar_wait(bar(kBSFull), it & 1u, abort_flag) ||
+                        !mbar_wait(bar(kBQdoFull + st), (it >> 1) & 1u, abort_flag)) {
+                        if (lane == 0) report_timeout(p.status, 2, static_cast<uint32_t>(warp), it, 400);
+                        ok = false;
+                    }
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    tc_fence_after();
+                    float pr[64];
+                    {
+                        uint32_t s[64];
+                        tmem_ld32(tST + lane_base + 64u * h, reinterpret_cast<uint32_t(&)[32]>(s[0]));
+                        tmem_ld32(tST + lane_base + 64u * h + 32u, reinterpret_cast<uint32_t(&)[32]>(s[32]));
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 64; ++j)
+                            pr[j] = ex2_approx(fmaf(__uint_as_float(s[j]), c, -ld[j].x));
+                    }
+                    if (w != 0xffffu) {
+#pragma unroll
+                        for (int j = 0; j < 64; ++j)
+                            if (!((w >> (mbit0 + ((64 * h + j) >> 4))) & 1u)) pr[j] = 0.f;
+                    }
+#pragma unroll
+                    for (int cc = 0; cc < 2; ++cc) {
+                        uint32_t pk[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) pk[j] = pack_bf16x2(pr[32 * cc + 2 * j], pr[32 * cc + 2 * j + 1]);
+                        tmem_st16(tST + lane_base + 64u * h + 16u * cc, pk);
+                    }
+                    tmem_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(bar(kBPReady));
+
+                    if (!mbar_wait(bar(kBDpFull), it & 1u, abort_flag)) {
+                        if (lane == 0) report_timeout(p.status, 2, static_cast<uint32_t>(warp), it, 401);
+                        ok = false;
+                    }
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    tc_fence_after();
+                    uint8_t* ds_row = base_ptr + kBwdSmemDS + static_cast<uint32_t>(h) * kPanelBytes +
+                                      static_cast<uint32_t>(row) * 128u;
+#pragma unroll
+                    for (int cc = 0; cc < 2; ++cc) {
+                        uint32_t dp[32];
+                        tmem_ld32(tDP + lane_base + 64u * h + 32u * cc, dp);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            uint32_t wds[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const int col = 32 * cc + 8 * q4 + 2 * j;
+                                const float d0 = pr[col] * (__uint_as_float(dp[8 * q4 + 2 * j]) - ld[col].y) * kSoftmaxScale;
+                                const float d1 = pr[col + 1] * (__uint_as_float(dp[8 * q4 + 2 * j + 1]) - ld[col + 1].y) * kSoftmaxScale;
+                                wds[j] = pack_bf16x2(d0, d1);
+                            }
+                            const int chunk = cc * 4 + q4;  // 16-byte chunk 0..7 of this 128-byte row
+                            *reinterpret_cast<uint4*>(ds_row + (static_cast<uint32_t>(chunk ^ (row & 7)) << 4)) =
+                                make_uint4(wds[0], wds[1], wds[2], wds[3]);
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    tc_fence_before();
+                    mbar_arrive(bar(kBDsReady));
+                }
+            }
+        }
+
+        // Epilogue: warps 0-3 write dV, warps 4-7 write dK (bf16, through swizzled staging + TMA).
+        if (n_total > 0 && ok) {
+            if (!mbar_wait(bar(kBDkvDone), 0, abort_flag)) {
+                if (lane == 0) report_timeout(p.status, 2, static_cast<uint32_t>(warp), 0, 500);
+                ok = false;
+            }
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        const uint32_t stage_off = h == 0 ? kBwdSmemQ : kBwdSmemDO;
+        if (ok) {
+            tc_fence_after();
+            const uint32_t tsrc = (h == 0 ? tDV : tDK) + lane_base;
+            uint8_t* stage = base_ptr + stage_off;
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+                uint32_t v[32];
+                if (n_total > 0) {
+                    tmem_ld32(tsrc + 32u * cc, v);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = 0u;
+                }
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    uint4 wv;
+                    wv.x = pack_bf16x2(__uint_as_float(v[8 * q4 + 0]), __uint_as_float(v[8 * q4 + 1]));
+                    wv.y = pack_bf16x2(__uint_as_float(v[8 * q4 + 2]), __uint_as_float(v[8 * q4 + 3]));
+                    wv.z = pack_bf16x2(__uint_as_float(v[8 * q4 + 4]), __uint_as_float(v[8 * q4 + 5]));
+                    wv.w = pack_bf16x2(__uint_as_float(v[8 * q4 + 6]), __uint_as_float(v[8 * q4 + 7]));
+                    const int chunk = cc * 4 + q4;
+                    const uint32_t o = static_cast<uint32_t>(chunk >> 3) * kPanelBytes +
+                                       static_cast<uint32_t>(row) * 128u +
+                                       (static_cast<uint32_t>((chunk & 7) ^ (row & 7)) << 4);
+                    *reinterpret_cast<uint4*>(stage + o) = wv;
+                }
+            }
+            fence_proxy_async_smem();
+        }
+        named_bar_sync(1 + h, 128);
+        if (ok && quad == 0 && lane == 0) {
+            const CUtensorMap* tm = h == 0 ? &tm_dv : &tm_dk;
+            tma_store_3d(tm, 0, nt * 128, bhk, base + stage_off);
+            tma_store_3d(tm, 64, nt * 128, bhk, base + stage_off + kPanelBytes);
+            tma_commit_group();
+            tma_wait_group0();
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 12) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+}  // namespace fba
+
 using namespace fba;
-extern "C" int fba_bwd_scratch_bytes(int B, int Hq, int Sq, uint64_t* lse_delta_bytes, uint64_t* dq_accum_bytes) {
+
+extern "C" int fba_bwd_scratch_bytes(int B, int Hq, int Sq, uint64_t* lse_delta_bytes,
+                                     uint64_t* dq_accum_bytes) {
     if (B <= 0 || Hq <= 0 || Sq <= 0 || !lse_delta_bytes || !dq_accum_bytes)
         return set_error(FBA_ERR_BAD_ARG, "fba_bwd_scratch_bytes: bad argument");
     const uint64_t rows = static_cast<uint64_t>(B) * Hq * ((Sq + 127) / 128) * 128;
@@ -8,6 +506,76 @@ extern "C" int fba_bwd_scratch_bytes(int B, int Hq, int Sq, uint64_t* lse_delta_
     *dq_accum_bytes = rows * 128 * sizeof(float);
     return FBA_OK;
 }
-extern "C" int fba_bwd(const void*, const void*, const void*, const void*, const float*, const void*, void*, void*, void*, int, int, int, int, int, const fba_list_t*, float*, float*, uint32_t*, void*) {
-    return set_error(FBA_ERR_BAD_ARG, "fba_bwd: not built yet");
+
+extern "C" int fba_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                       const void* dout, void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int Sq,
+                       int Skv, const fba_list_t* k2q, float* lse_delta, float* dq_accum,
+                       uint32_t* status, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!q || !k || !v || !o || !lse || !dout || !dq || !dk || !dv || !lse_delta || !dq_accum || !status)
+        return set_error(FBA_ERR_BAD_ARG, "fba_bwd: null pointer argument");
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || Sq <= 0 || Skv <= 0)
+        return set_error(FBA_ERR_BAD_ARG, "fba_bwd: non-positive size");
+    if (Hq % Hkv != 0) return set_error(FBA_ERR_BAD_ARG, "fba_bwd: Hq must be a multiple of Hkv");
+    if (Sq < 128 || Skv < 128)
+        return set_error(FBA_ERR_BAD_ARG, "fba_bwd: sequence lengths below 128 are not supported");
+    if (!k2q || !k2q->idx || !k2q->cnt || k2q->stride <= 0 || k2q->rows_per_bh <= 0 || k2q->rows_div <= 0 ||
+        k2q->sub <= 0 || (k2q->bh_stride != 0 && k2q->bh_stride != k2q->rows_per_bh))
+        return set_error(FBA_ERR_BAD_ARG, "fba_bwd: malformed k2q list");
+    const int n_mtiles = (Sq + 127) / 128;
+    const int n_ntiles = (Skv + 127) / 128;
+    if (static_cast<long long>(k2q->rows_per_bh) * k2q->rows_div < n_ntiles ||
+        static_cast<long long>(k2q->stride) * k2q->sub < n_mtiles)
+        return set_error(FBA_ERR_BAD_ARG, "fba_bwd: k2q list does not cover the sequences");
+    if (static_cast<long long>(B) * Hq > 65535)
+        return set_error(FBA_ERR_TOO_LARGE, "fba_bwd: B * Hq exceeds 65535");
+
+    const long long n_bhq = static_cast<long long>(B) * Hq, n_bhk = static_cast<long long>(B) * Hkv;
+    CUtensorMap tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv;
+    int rc;
+    if ((rc = make_tmap_bf16(&tm_q, q, Sq, n_bhq, 128)) != FBA_OK) return rc;
+    if ((rc = make_tmap_bf16(&tm_k, k, Skv, n_bhk, 128)) != FBA_OK) return rc;
+    if ((rc = make_tmap_bf16(&tm_v, v, Skv, n_bhk, 128)) != FBA_OK) return rc;
+    if ((rc = make_tmap_bf16(&tm_do, dout, Sq, n_bhq, 128)) != FBA_OK) return rc;
+    if ((rc = make_tmap_bf16(&tm_dk, dk, Skv, n_bhk, 128)) != FBA_OK) return rc;
+    if ((rc = make_tmap_bf16(&tm_dv, dv, Skv, n_bhk, 128)) != FBA_OK) return rc;
+
+    const int rows_pad = n_mtiles * 128;
+    const long long total_rows = n_bhq * rows_pad;
+    {
+        const long long blocks = (total_rows * 32 + 255) / 256;
+        bwd_prep_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+            static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dout), lse,
+            reinterpret_cast<float2*>(lse_delta), Sq, rows_pad, total_rows);
+        if ((rc = check_launch("bwd_prep_kernel")) != FBA_OK) return rc;
+    }
+    if (cudaMemsetAsync(dq_accum, 0, static_cast<size_t>(total_rows) * 128 * sizeof(float), stream) != cudaSuccess) {
+        cudaGetLastError();
+        return set_error(FBA_ERR_LAUNCH, "fba_bwd: cudaMemsetAsync failed");
+    }
+    {
+        cudaError_t e = cudaFuncSetAttribute(fba_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(kBwdSmemBytes));
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return set_error(FBA_ERR_LAUNCH, "fba_bwd: cannot raise the dynamic shared memory limit");
+        }
+        BwdParams p;
+        p.list = to_dev(*k2q);
+        p.ld = reinterpret_cast<const float2*>(lse_delta);
+        p.dq_accum = dq_accum;
+        p.status = status;
+        p.n_mtiles = n_mtiles;
+        p.Hq = Hq;
+        p.Hkv = Hkv;
+        dim3 grid(n_ntiles, static_cast<unsigned>(n_bhk));
+        fba_bwd_kernel<<<grid, kBwdThreads, kBwdSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv, p);
+        if ((rc = check_launch("fba_bwd_kernel")) != FBA_OK) return rc;
+    }
+    {
+        dim3 grid(n_mtiles, static_cast<unsigned>(n_bhq));
+        bwd_dq_convert_kernel<<<grid, 256, 0, stream>>>(dq_accum, static_cast<__nv_bfloat16*>(dq), Sq, n_mtiles);
+        if ((rc = check_launch("bwd_dq_convert_kernel")) != FBA_OK) return rc;
+    }
+    return FBA_OK;
 }
