@@ -17,6 +17,8 @@ LIB_PATH = Path(__file__).resolve().parent / "libfba_b200.so"
 EXPORTED_SYMBOLS = (
     "fba_abi_version",
     "fba_last_error",
+    "fba_launch_count",
+    "fba_set_timing_events",
     "fba_build_index",
     "fba_build_tile_lists",
     "fba_fwd",
@@ -60,6 +62,10 @@ def lib() -> ctypes.CDLL:
     L.fba_abi_version.argtypes = []
     L.fba_last_error.restype = ctypes.c_char_p
     L.fba_last_error.argtypes = []
+    L.fba_launch_count.restype = ctypes.c_uint64
+    L.fba_launch_count.argtypes = []
+    L.fba_set_timing_events.restype = i32
+    L.fba_set_timing_events.argtypes = [i32, vp, vp]
     L.fba_build_index.restype = i32
     L.fba_build_index.argtypes = [vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp]
     L.fba_build_tile_lists.restype = i32

@@ -13,9 +13,22 @@ int set_error(int code, const char* msg) {
     return code;
 }
 
+static unsigned long long g_launches = 0;
+static thread_local cudaEvent_t g_ev_start = nullptr, g_ev_stop = nullptr;
+static thread_local int g_ev_which = 0;
+
+void timing_mark(int which, bool start, cudaStream_t stream) {
+    if (which != g_ev_which) return;
+    cudaEvent_t ev = start ? g_ev_start : g_ev_stop;
+    if (ev) cudaEventRecord(ev, stream);
+}
+
 int check_launch(const char* what) {
     cudaError_t e = cudaGetLastError();
-    if (e == cudaSuccess) return FBA_OK;
+    if (e == cudaSuccess) {
+        __atomic_fetch_add(&g_launches, 1ull, __ATOMIC_RELAXED);
+        return FBA_OK;
+    }
     snprintf(g_err, sizeof(g_err), "%s: %s", what, cudaGetErrorString(e));
     return FBA_ERR_LAUNCH;
 }
@@ -64,4 +77,14 @@ int make_tmap_bf16(CUtensorMap* out, const void* base, int seq, long long n_bh, 
 }  // namespace fba
 
 extern "C" int fba_abi_version(void) { return FBA_ABI_VERSION; }
+extern "C" uint64_t fba_launch_count(void) { return __atomic_load_n(&fba::g_launches, __ATOMIC_RELAXED); }
+extern "C" int fba_set_timing_events(int which, void* start_event, void* stop_event) {
+    if (which < 0 || which > 2) return fba::set_error(FBA_ERR_BAD_ARG, "fba_set_timing_events: which must be 0, 1 or 2");
+    if (which != 0 && (!start_event || !stop_event))
+        return fba::set_error(FBA_ERR_BAD_ARG, "fba_set_timing_events: null event");
+    fba::g_ev_which = which;
+    fba::g_ev_start = static_cast<cudaEvent_t>(start_event);
+    fba::g_ev_stop = static_cast<cudaEvent_t>(stop_event);
+    return FBA_OK;
+}
 extern "C" const char* fba_last_error(void) { return fba::g_err; }

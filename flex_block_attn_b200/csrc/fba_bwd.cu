@@ -569,8 +569,11 @@ extern "C" int fba_bwd(const void* q, const void* k, const void* v, const void* 
         p.Hq = Hq;
         p.Hkv = Hkv;
         dim3 grid(n_ntiles, static_cast<unsigned>(n_bhk));
+        timing_mark(2, true, stream);
         fba_bwd_kernel<<<grid, kBwdThreads, kBwdSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv, p);
-        if ((rc = check_launch("fba_bwd_kernel")) != FBA_OK) return rc;
+        rc = check_launch("fba_bwd_kernel");
+        timing_mark(2, false, stream);
+        if (rc != FBA_OK) return rc;
     }
     {
         dim3 grid(n_mtiles, static_cast<unsigned>(n_bhq));

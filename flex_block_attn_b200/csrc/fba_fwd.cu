@@ -429,6 +429,9 @@ extern "C" int fba_fwd(const void* q, const void* k, const void* v, void* o, flo
     p.Hq = Hq;
     p.Hkv = Hkv;
     dim3 grid((n_mtiles + 1) / 2, B * Hq);
+    timing_mark(1, true, stream);
     fba_fwd_kernel<<<grid, kFwdThreads, kFwdSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, p);
-    return check_launch("fba_fwd_kernel");
+    rc = check_launch("fba_fwd_kernel");
+    timing_mark(1, false, stream);
+    return rc;
 }

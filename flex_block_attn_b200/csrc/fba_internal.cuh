@@ -14,6 +14,10 @@ int set_error(int code, const char* msg);
 // cudaGetLastError() after a launch; returns FBA_OK or FBA_ERR_LAUNCH (with text recorded).
 int check_launch(const char* what);
 
+// Record the caller-supplied timing event (fba_set_timing_events) around main kernel `which`
+// (1 = forward, 2 = backward); no-op unless that kernel was selected on this thread.
+void timing_mark(int which, bool start, cudaStream_t stream);
+
 // 3-D bf16 tensor map over a [n_bh, seq, 128] tensor viewed as (col, row, bh), box = 64 columns x
 // `box_rows` rows x 1, 128-byte swizzle, out-of-range rows read as zero and are dropped on store.
 int make_tmap_bf16(CUtensorMap* out, const void* base, int seq, long long n_bh, int box_rows);

@@ -67,6 +67,18 @@ int fba_abi_version(void);
 /* Text of the most recent error on the calling thread ("" if none). */
 const char* fba_last_error(void);
 
+/* Number of kernels this library has launched in this process (all threads). */
+uint64_t fba_launch_count(void);
+/*
+ * Measurement hook (no counterpart in the reference, which times whole calls from Python with
+ * do_bench, benchmark/dynamic/random/scripts/random_fwd.py:161-166).  After
+ * fba_set_timing_events(which, e0, e1) the calling thread's later fba_fwd (which = 1) or fba_bwd
+ * (which = 2) calls record the CUDA events e0 / e1 (cudaEvent_t) on their stream immediately
+ * before / after the main attention kernel, so its duration can be read without the small
+ * helper kernels around it.  which = 0 switches the hook off.
+ */
+int fba_set_timing_events(int which, void* start_event, void* stop_event);
+
 /*
  * Block-mask -> index-list compaction (integer work, bit-exact against a nonzero()-based
  * restatement).  Replaces the per-call mask pooling and transposes of the reference's Python layer

@@ -1,0 +1,59 @@
+"""CPU: the Python layer keeps the reference's argument checks (flex_block_attn_interface.py:18-32)
+and refuses CPU tensors instead of falling back."""
+import pytest
+import torch
+
+import flex_block_attn_b200 as fba
+from flex_block_attn_b200 import masks
+
+
+def _qkv(S=256, H=1):
+    q = torch.zeros((1, H, S, 128), dtype=torch.bfloat16)
+    return q, q.clone(), q.clone()
+
+
+@pytest.mark.parametrize("qb,kb,msg", [
+    (24, 64, "q_block_size (24) must be divisible by 16"),
+    (16, 96, "kv_block_size (96) must be divisible by 64"),
+    (48, 64, "must be divisible by q_block_size (48), or vice versa"),
+])
+def test_block_size_assertions(qb, kb, msg):
+    q, k, v = _qkv()
+    with pytest.raises(AssertionError) as e:
+        fba.flex_block_attn_func(q, k, v, qb, kb, torch.ones((2, 2), dtype=torch.bool))
+    assert msg in str(e.value)
+
+
+def test_length_and_mask_shape_assertions():
+    q, k, v = _qkv(S=200)
+    with pytest.raises(AssertionError, match="q_seq_len \\(200\\) must be divisible by q_block_size"):
+        fba.flex_block_attn_func(q, k, v, 128, 128, torch.ones((2, 2), dtype=torch.bool))
+    q, k, v = _qkv(S=256)
+    with pytest.raises(AssertionError, match="must equal q_seq_len"):
+        fba.flex_block_attn_func(q, k, v, 128, 128, torch.ones((3, 2), dtype=torch.bool))
+
+
+def test_cpu_tensors_are_refused_not_emulated():
+    q, k, v = _qkv()
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        fba.flex_block_attn_func(q, k, v, 128, 128, torch.ones((2, 2), dtype=torch.bool))
+
+
+def test_mask_builders_on_cpu():
+    m = masks.sta_mask((3, 6, 10), device="cpu")
+    assert m.shape == (180, 180) and int(m.sum()) == 3136 and bool((m == m.T).all())
+    assert int(m.sum(1).min()) == 8 and int(m.sum(1).max()) == 27
+    perm = masks.tile_major_permutation((18, 48, 80), (6, 8, 8))
+    assert perm.shape == (69120,) and torch.equal(torch.sort(perm).values, torch.arange(69120))
+    first = perm[:384]
+    t, h, w = first // (48 * 80), (first // 80) % 48, first % 80
+    assert int(t.max()) == 5 and int(h.max()) == 7 and int(w.max()) == 7
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn((1, 2, 3 * 128 * 2, 128), generator=g)
+    k = torch.randn((1, 2, 2 * 384, 128), generator=g)
+    mb = masks.moba_topk_mask(q, k, 128, 384, 1)
+    assert mb.shape == (1, 2, 6, 2) and bool((mb.sum(-1) == 1).all())
+    ms = masks.ssta_mask(q, k, (1, 1, 2), 128, 384, topk=1, window=(0, 0, 0))
+    assert ms.shape == (1, 2, 6, 2) and bool(ms[0, 0, 0, 0]) and bool(ms[0, 0, 5, 1])
+    bm = masks.bernoulli_mask(1, 2, 6, 3, 0.0, 0, device="cpu")
+    assert int(bm.sum()) == 12  # only the forced (scaled) diagonal
