@@ -33,6 +33,19 @@ int check_launch(const char* what) {
     return FBA_ERR_LAUNCH;
 }
 
+int bind_device_of(const void* ptr) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, ptr) != cudaSuccess || a.type != cudaMemoryTypeDevice) {
+        cudaGetLastError();
+        return set_error(FBA_ERR_BAD_ARG, "pointer is not device memory");
+    }
+    if (cudaSetDevice(a.device) != cudaSuccess) {
+        cudaGetLastError();
+        return set_error(FBA_ERR_LAUNCH, "cudaSetDevice failed for the device that owns the buffers");
+    }
+    return FBA_OK;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,

@@ -533,6 +533,7 @@ extern "C" int fba_bwd(const void* q, const void* k, const void* v, const void* 
     const long long n_bhq = static_cast<long long>(B) * Hq, n_bhk = static_cast<long long>(B) * Hkv;
     CUtensorMap tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv;
     int rc;
+    if ((rc = bind_device_of(q)) != FBA_OK) return rc;
     if ((rc = make_tmap_bf16(&tm_q, q, Sq, n_bhq, 128)) != FBA_OK) return rc;
     if ((rc = make_tmap_bf16(&tm_k, k, Skv, n_bhk, 128)) != FBA_OK) return rc;
     if ((rc = make_tmap_bf16(&tm_v, v, Skv, n_bhk, 128)) != FBA_OK) return rc;

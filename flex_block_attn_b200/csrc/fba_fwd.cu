@@ -398,6 +398,7 @@ extern "C" int fba_fwd(const void* q, const void* k, const void* v, void* o, flo
         return set_error(FBA_ERR_BAD_ARG, "fba_fwd: sequence lengths below 128 are not supported");
     int rc = check_list(q2k, "fba_fwd: malformed q2k list");
     if (rc != FBA_OK) return rc;
+    if ((rc = bind_device_of(q)) != FBA_OK) return rc;
     const int n_mtiles = (Sq + 127) / 128;
     const int n_ntiles = (Skv + 127) / 128;
     if (static_cast<long long>(q2k->rows_per_bh) * q2k->rows_div < n_mtiles ||

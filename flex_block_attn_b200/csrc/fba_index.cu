@@ -118,7 +118,8 @@ extern "C" int fba_build_index(const uint8_t* mask, int mask_dim, int B, int H, 
         return set_error(FBA_ERR_BAD_ARG, "fba_build_index: idx and cnt must be given together");
     const int n_bh = mask_dim == 4 ? B * H : 1;
     const long long bh_stride = mask_dim == 4 ? static_cast<long long>(nQ) * nK : 0;
-    int rc = FBA_OK;
+    int rc = bind_device_of(mask);
+    if (rc != FBA_OK) return rc;
     if (q2k_idx) {
         BlockPred<false> p{mask, bh_stride, nQ, nK};
         rc = launch_compact(p, n_bh, nQ, nK, q2k_idx, q2k_cnt, nullptr, stream);
@@ -153,7 +154,8 @@ extern "C" int fba_build_tile_lists(const uint8_t* mask, int mask_dim, int B, in
     const int n_bh = mask_dim == 4 ? B * H : 1;
     const long long bh_stride = mask_dim == 4 ? static_cast<long long>(nQ) * nK : 0;
     const int nMt = (Sq + 127) / 128, nNt = (Skv + 127) / 128;
-    int rc = FBA_OK;
+    int rc = bind_device_of(mask);
+    if (rc != FBA_OK) return rc;
     if (want_fwd) {
         TilePred<false> p{mask, bh_stride, nQ, nK, q_block, kv_block, Sq, Skv};
         rc = launch_compact(p, n_bh, nMt, nNt, fwd_idx, fwd_cnt, fwd_msk, stream);

@@ -14,6 +14,11 @@ int set_error(int code, const char* msg);
 // cudaGetLastError() after a launch; returns FBA_OK or FBA_ERR_LAUNCH (with text recorded).
 int check_launch(const char* what);
 
+// Make the device that owns `ptr` current on the calling thread.  Callers may arrive on threads
+// that never touched CUDA (e.g. an autograd worker), where no context is current yet and the
+// driver-level tensor-map encoder would fail.
+int bind_device_of(const void* ptr);
+
 // Record the caller-supplied timing event (fba_set_timing_events) around main kernel `which`
 // (1 = forward, 2 = backward); no-op unless that kernel was selected on this thread.
 void timing_mark(int which, bool start, cudaStream_t stream);

@@ -143,8 +143,9 @@ def test_bad_inputs_raise():
     m = torch.ones((2, 2), dtype=torch.bool, device="cuda")
     with pytest.raises(TypeError):
         fba.flex_block_attn_func(q.float(), k, v, 128, 128, m)
+    q_nc = torch.zeros((1, 256, 2, 128), dtype=torch.bfloat16, device="cuda").transpose(1, 2)
+    assert not q_nc.is_contiguous()
     with pytest.raises(RuntimeError, match="contiguous"):
-        fba.flex_block_attn_func(q.transpose(1, 2).contiguous().transpose(1, 2), k, v, 128, 128, m) if False else \
-            fba.flex_block_attn_func(torch.empty((1, 256, 1, 128), dtype=torch.bfloat16, device="cuda").transpose(1, 2), k, v, 128, 128, m)
+        fba.flex_block_attn_func(q_nc, k, v, 128, 128, m)
     with pytest.raises(TypeError):
         fba.flex_block_attn_func(q, k, v, 128, 128, m.to(torch.uint8))
