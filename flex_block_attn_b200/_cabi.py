@@ -24,6 +24,8 @@ EXPORTED_SYMBOLS = (
     "fba_fwd",
     "fba_bwd_scratch_bytes",
     "fba_bwd",
+    "fba_bwd_static_scratch_max_rows",
+    "fba_bwd_static_scratch",
 )
 
 
@@ -76,6 +78,10 @@ def lib() -> ctypes.CDLL:
     L.fba_bwd_scratch_bytes.argtypes = [i32, i32, i32, ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]
     L.fba_bwd.restype = i32
     L.fba_bwd.argtypes = [vp] * 9 + [i32] * 5 + [ctypes.POINTER(FbaList), vp, vp, vp, vp]
+    L.fba_bwd_static_scratch_max_rows.restype = ctypes.c_uint64
+    L.fba_bwd_static_scratch_max_rows.argtypes = []
+    L.fba_bwd_static_scratch.restype = i32
+    L.fba_bwd_static_scratch.argtypes = [vp] * 9 + [i32] * 5 + [ctypes.POINTER(FbaList), vp, vp]
     if L.fba_abi_version() != 1:
         raise RuntimeError("libfba_b200.so has an unexpected ABI version")
     _LIB = L

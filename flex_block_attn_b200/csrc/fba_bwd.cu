@@ -583,3 +583,66 @@ extern "C" int fba_bwd(const void* q, const void* k, const void* v, const void* 
     }
     return FBA_OK;
 }
+
+// ------------------------------------------------------------------------------------------
+// Backward without caller-provided scratch.
+//
+// Some hosts of this library may not allocate device memory at the moment they need a backward
+// pass: a serving or training process that handed all of its HBM to a fixed arena at start-up, a
+// plugin that runs inside someone else's memory pool, or code on a latency-critical path where
+// cudaMalloc's implicit device synchronisation is not acceptable.  For them the two scratch
+// buffers of fba_bwd live in a fixed device array that is part of the library image.  Every GPU
+// whose context loads the library carries this array until the process exits.
+//
+// Capacity: kStaticScratchRows padded query rows in total (B * Hq * ceil(Sq/128) * 128), each row
+// needing 2 floats of (lse, delta) and 128 floats of dQ accumulator.
+constexpr unsigned long long kStaticScratchRows = 131072;  // e.g. B*Hq = 8 at Sq = 16384
+constexpr unsigned long long kStaticLdBytes = kStaticScratchRows * 2 * sizeof(float);
+constexpr unsigned long long kStaticAccBytes = kStaticScratchRows * 128 * sizeof(float);
+static __device__ __align__(256) unsigned char g_bwd_static_scratch[kStaticLdBytes + kStaticAccBytes];
+
+constexpr int kMaxDevices = 64;
+static unsigned char* g_static_scratch_addr[kMaxDevices];  // device address per device ordinal
+
+extern "C" uint64_t fba_bwd_static_scratch_max_rows(void) { return kStaticScratchRows; }
+
+extern "C" int fba_bwd_static_scratch(const void* q, const void* k, const void* v, const void* o,
+                                      const float* lse, const void* dout, void* dq, void* dk, void* dv,
+                                      int B, int Hq, int Hkv, int Sq, int Skv, const fba_list_t* k2q,
+                                      uint32_t* status, void* stream) {
+    if (!q) return set_error(FBA_ERR_BAD_ARG, "fba_bwd_static_scratch: null pointer argument");
+    if (B <= 0 || Hq <= 0 || Sq <= 0)
+        return set_error(FBA_ERR_BAD_ARG, "fba_bwd_static_scratch: non-positive size");
+    const unsigned long long rows =
+        static_cast<unsigned long long>(B) * Hq * ((static_cast<unsigned long long>(Sq) + 127) / 128) * 128;
+    if (rows > kStaticScratchRows)
+        return set_error(FBA_ERR_TOO_LARGE,
+                         "fba_bwd_static_scratch: B * Hq * ceil(Sq/128) * 128 exceeds the built-in scratch "
+                         "capacity of 131072 rows; use fba_bwd with caller-allocated scratch");
+    int rc = bind_device_of(q);
+    if (rc != FBA_OK) return rc;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        cudaGetLastError();
+        return set_error(FBA_ERR_LAUNCH, "fba_bwd_static_scratch: cannot identify the current device");
+    }
+    // The array's name is only a host-side handle; the kernels need its device address, which
+    // is looked up once per device (with that device current) and cached.
+    unsigned char* base = __atomic_load_n(&g_static_scratch_addr[dev], __ATOMIC_ACQUIRE);
+    if (!base) {
+        void* sym = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&sym, g_bwd_static_scratch);
+        if (e != cudaSuccess || !sym) {
+            cudaGetLastError();
+            return set_error(FBA_ERR_LAUNCH, "fba_bwd_static_scratch: cudaGetSymbolAddress failed");
+        }
+        base = static_cast<unsigned char*>(sym);
+        __atomic_store_n(&g_static_scratch_addr[dev], base, __ATOMIC_RELEASE);
+    }
+    float* lse_delta = reinterpret_cast<float*>(base);
+    float* dq_accum = reinterpret_cast<float*>(base + kStaticLdBytes);
+    // fba_bwd overwrites the (lse, delta) region and zero-fills the part of the accumulator it
+    // uses before accumulating, so nothing left over from an earlier call is read.
+    return fba_bwd(q, k, v, o, lse, dout, dq, dk, dv, B, Hq, Hkv, Sq, Skv, k2q, lse_delta, dq_accum, status,
+                   stream);
+}

@@ -127,6 +127,31 @@ int fba_bwd(const void* q, const void* k, const void* v, const void* o, const fl
             int Skv, const fba_list_t* k2q, float* lse_delta, float* dq_accum, uint32_t* status,
             void* stream);
 
+/*
+ * Backward for callers that cannot allocate device memory (no counterpart in the reference, whose
+ * extension allocates everything it needs through torch, .cu:1077-1093).
+ *
+ * Same computation and results as fba_bwd, but the two scratch buffers come from a fixed array
+ * built into the library instead of from the caller: meant for hosts whose HBM is fully owned by
+ * a pre-sized arena or a foreign memory pool, or that must avoid cudaMalloc's device-wide
+ * synchronisation on a latency-critical path.  The call itself allocates nothing.
+ *   - Limit: B * Hq * ceil(Sq/128) * 128 <= fba_bwd_static_scratch_max_rows() (131072 rows, i.e.
+ *     about 65 MiB that every GPU loading this library keeps resident until the process exits).
+ *     Larger problems return FBA_ERR_TOO_LARGE; use fba_bwd for those.
+ *   - The first call on each device looks up the array's device address (one
+ *     cudaGetSymbolAddress with that device current); make that first call outside any stream
+ *     capture.
+ *   - All calls on a device share the one array, and it keeps whatever the previous call left;
+ *     each call rewrites / zero-fills the part it uses before reading it.  Two calls whose
+ *     kernels may overlap on the GPU (different streams, or several host threads) race on it:
+ *     serialise them.
+ */
+uint64_t fba_bwd_static_scratch_max_rows(void);
+int fba_bwd_static_scratch(const void* q, const void* k, const void* v, const void* o,
+                           const float* lse, const void* dout, void* dq, void* dk, void* dv, int B,
+                           int Hq, int Hkv, int Sq, int Skv, const fba_list_t* k2q, uint32_t* status,
+                           void* stream);
+
 #ifdef __cplusplus
 }
 #endif
