@@ -10,50 +10,58 @@
 //                             S^T  = K Q^T          (smem x smem -> TMEM)
 //                             dP^T = V dO^T         (smem x smem -> TMEM)
 //                             dV  += P^T dO         (P^T bf16 in TMEM x smem)
-//                             dK  += dS^T Q         (dS^T bf16 in smem x smem)
-//                             dQ   = dS K           (smem x smem -> TMEM, then fp32 red.add to HBM)
+//                             dQ   = dS K           (dS^T bf16 in smem, MN-major x smem -> TMEM)
+//                             dK  += dS^T Q         (dS^T bf16 in smem, K-major x smem)
 //                           TMEM columns: [0,128) S^T / P^T, [128,256) dV, [256,384) dP^T then dQ,
 //                           [384,512) dK.  dK and dV stay in TMEM for the whole CTA (and across
 //                           the query heads of a grouped-query group), so they are written once,
 //                           in bf16, with no atomics; the reference reduce-adds fp32 tiles
 //                           (.cu:544-570) into zero-filled buffers (.cu:1077-1088).
+//                           dQ tiles leave TMEM into registers and are added to an fp32
+//                           accumulator with 16-byte vector reductions (red.global.add.v4.f32).
 //   3. bwd_dq_convert_kernel  dQ fp32 accumulator (tile-blocked layout) -> bf16 [B,H,Sq,128].
 //
 // Warp roles of the main kernel (448 threads): warps 0-7 compute P^T and dS^T (thread = key row;
 // warps 0-3 take query columns 0-63 of the tile, warps 4-7 columns 64-127), warps 8-11 drain dQ
-// from TMEM and issue the vector reductions, warp 12 issues every MMA, warp 13 drives TMA.
+// from TMEM, warp 12 issues every MMA, warp 13 drives TMA.
+//
+// Shared memory: K, V resident (64 KiB); Q double-buffered with its (lse2, delta) rows (64 + 2 KiB);
+// dO single-buffered (32 KiB; it is reloaded between dV of one query tile and dP^T of the next);
+// dS^T (32 KiB).
 #include "fba_common.cuh"
 
 namespace fba {
 
-constexpr int kBwdThreads = 448;
+constexpr int kBwdThreads = 512;  // 4 warpgroups: compute, compute, dQ drain, {MMA, TMA, 2 idle}
 constexpr uint32_t kBwdSmemK = 0;
 constexpr uint32_t kBwdSmemV = 1 * kTileBytes;
 constexpr uint32_t kBwdSmemQ = 2 * kTileBytes;    // 2 stages
-constexpr uint32_t kBwdSmemDO = 4 * kTileBytes;   // 2 stages
-constexpr uint32_t kBwdSmemDS = 6 * kTileBytes;
-constexpr uint32_t kBwdSmemLD = 7 * kTileBytes;   // 2 stages x 128 x (lse2, delta)
+constexpr uint32_t kBwdSmemDO = 4 * kTileBytes;   // 1 stage
+constexpr uint32_t kBwdSmemDS = 5 * kTileBytes;
+constexpr uint32_t kBwdSmemLD = 7 * kTileBytes;     // 2 stages x 128 x (lse2, delta)
 constexpr uint32_t kBwdSmemBars = kBwdSmemLD + 2 * 1024;
 constexpr uint32_t kBwdSmemBytes = kBwdSmemBars + 128;
 
 enum BwdBar : uint32_t {
     kBKvFull = 0,
-    kBQdoFull = 1,    // 2
-    kBQdoEmpty = 3,   // 2
-    kBSFull = 5,
-    kBPReady = 6,
-    kBDpFull = 7,
-    kBDsReady = 8,
-    kBDqFull = 9,
-    kBDqDrained = 10,
-    kBDkvDone = 11,
-    kBCount = 12
+    kBQFull = 1,      // 2
+    kBQEmpty = 3,     // 2
+    kBDoFull = 5,
+    kBDoEmpty = 6,
+    kBSFull = 7,
+    kBPReady = 8,
+    kBDpFull = 9,
+    kBDsReady = 10,
+    kBDqFull = 11,
+    kBDqDrained = 12,
+    kBDkvDone = 13,
+    kBCount = 14
 };
 
 struct BwdParams {
     ListDev list;          // key-major: rows = key tiles / rows_div, entries = query tiles / sub
     const float2* ld;      // [B*Hq, nMt*128] (lse * log2e, delta)
-    float* dq_accum;       // [B*Hq, nMt, 32, 128, 4]
+    float* dq_accum;       // [B*Hq, nMt, 4 column chunks, 4 row groups, 8, 32, 4] fp32
     uint32_t* status;
     int n_mtiles, Hq, Hkv;
 };
@@ -94,6 +102,10 @@ __global__ void __launch_bounds__(256) bwd_prep_kernel(const __nv_bfloat16* __re
 }
 
 // ------------------------------------------------------------------------------------------
+// dQ accumulator layout: element (row = 32 w + r, col = 32 cc + 4 j + e) of query tile t sits at
+// float offset ((((t * 4 + cc) * 4 + w) * 8 + j) * 32 + r) * 4 + e, i.e. each (column chunk cc,
+// row group w) is a contiguous 4 KiB block owned by one drain warp, ordered so that the 32 lanes of a
+// vector reduction touch 512 consecutive bytes.
 __global__ void __launch_bounds__(256) bwd_dq_convert_kernel(const float* __restrict__ acc,
                                                             __nv_bfloat16* __restrict__ dq, int Sq,
                                                             int n_mtiles) {
@@ -103,13 +115,13 @@ __global__ void __launch_bounds__(256) bwd_dq_convert_kernel(const float* __rest
     const float4* src = reinterpret_cast<const float4*>(acc) + (bh * n_mtiles + mt) * (32LL * 128);
 #pragma unroll 4
     for (int k = 0; k < 16; ++k) {
-        const int i = threadIdx.x + 256 * k;  // (cg, row)
-        const int cg = i >> 7, row = i & 127;
+        const int i = threadIdx.x + 256 * k;
+        const int r = i & 31, j = (i >> 5) & 7, w = (i >> 8) & 3, cc = i >> 10;
         const float4 v = src[i];
-        uint2 w;
-        w.x = pack_bf16x2(v.x, v.y);
-        w.y = pack_bf16x2(v.z, v.w);
-        tile[row * 33 + cg] = w;
+        uint2 pk;
+        pk.x = pack_bf16x2(v.x, v.y);
+        pk.y = pack_bf16x2(v.z, v.w);
+        tile[(w * 32 + r) * 33 + cc * 8 + j] = pk;
     }
     __syncthreads();
 #pragma unroll 4
@@ -119,8 +131,8 @@ __global__ void __launch_bounds__(256) bwd_dq_convert_kernel(const float* __rest
         const int grow = mt * 128 + row;
         if (grow < Sq) {
             const uint2 a = tile[row * 33 + 2 * c], b = tile[row * 33 + 2 * c + 1];
-            uint4 w = make_uint4(a.x, a.y, b.x, b.y);
-            reinterpret_cast<uint4*>(dq + (bh * Sq + grow) * 128)[c] = w;
+            uint4 w4 = make_uint4(a.x, a.y, b.x, b.y);
+            reinterpret_cast<uint4*>(dq + (bh * Sq + grow) * 128)[c] = w4;
         }
     }
 }
@@ -151,7 +163,6 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
                  "f"(d)
                  : "memory");
 }
-
 __global__ void __launch_bounds__(kBwdThreads, 1)
 fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -190,9 +201,11 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         *abort_flag = 0;
         mbar_init(bar(kBKvFull), 1);
         for (int s = 0; s < 2; ++s) {
-            mbar_init(bar(kBQdoFull + s), 1);
-            mbar_init(bar(kBQdoEmpty + s), 1);
+            mbar_init(bar(kBQFull + s), 1);
+            mbar_init(bar(kBQEmpty + s), 1);
         }
+        mbar_init(bar(kBDoFull), 1);
+        mbar_init(bar(kBDoEmpty), 1);
         mbar_init(bar(kBSFull), 1);
         mbar_init(bar(kBPReady), 256);
         mbar_init(bar(kBDpFull), 1);
@@ -218,10 +231,16 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint32_t tmem = *tmem_slot;
     const uint32_t tST = tmem + 0, tDV = tmem + 128, tDP = tmem + 256, tDK = tmem + 384;
     const uint32_t sK = base + kBwdSmemK, sV = base + kBwdSmemV, sDS = base + kBwdSmemDS;
+    const uint32_t sDO = base + kBwdSmemDO;
     auto sQ = [&](int s) { return base + kBwdSmemQ + static_cast<uint32_t>(s) * kTileBytes; };
-    auto sDO = [&](int s) { return base + kBwdSmemDO + static_cast<uint32_t>(s) * kTileBytes; };
 
-    if (warp == 13) {
+    // Register budget: 512 threads x 128 at launch (the whole register file); the MMA/TMA
+    // warpgroup gives most of its share to the three warpgroups that hold tile rows in registers.
+    // The four budgets must not exceed 4 x 128 in total (152 * 3 + 56 = 512), or an increase would
+    // wait for registers that are never released.
+    if (warp >= 12) {
+      reg_dec<56>();
+      if (warp == 13) {
         // ------------------------------------------------------------------ TMA loader
         if (lane == 0 && n_total > 0) {
             mbar_expect_tx(bar(kBKvFull), 2 * kTileBytes);
@@ -239,20 +258,26 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     const int q0 = p.list.idx[lr * p.list.stride + e] * sub;
                     for (int u = 0; u < sub; ++u, ++it) {
                         const int st = it & 1;
-                        if (!mbar_wait(bar(kBQdoEmpty + st), ((it >> 1) & 1u) ^ 1u, abort_flag)) {
+                        const int qt = q0 + u;
+                        if (!mbar_wait(bar(kBQEmpty + st), ((it >> 1) & 1u) ^ 1u, abort_flag)) {
                             report_timeout(p.status, 2, 13, it, 100);
                             ok = false;
                             break;
                         }
-                        const int qt = q0 + u;
-                        mbar_expect_tx(bar(kBQdoFull + st), 2 * kTileBytes + 1024);
-                        tma_load_3d(sQ(st), &tm_q, 0, qt * 128, bq, bar(kBQdoFull + st));
-                        tma_load_3d(sQ(st) + kPanelBytes, &tm_q, 64, qt * 128, bq, bar(kBQdoFull + st));
-                        tma_load_3d(sDO(st), &tm_do, 0, qt * 128, bq, bar(kBQdoFull + st));
-                        tma_load_3d(sDO(st) + kPanelBytes, &tm_do, 64, qt * 128, bq, bar(kBQdoFull + st));
+                        mbar_expect_tx(bar(kBQFull + st), kTileBytes + 1024);
+                        tma_load_3d(sQ(st), &tm_q, 0, qt * 128, bq, bar(kBQFull + st));
+                        tma_load_3d(sQ(st) + kPanelBytes, &tm_q, 64, qt * 128, bq, bar(kBQFull + st));
                         bulk_load(base + kBwdSmemLD + st * 1024u,
                                   p.ld + (static_cast<long long>(bq) * p.n_mtiles + qt) * 128, 1024,
-                                  bar(kBQdoFull + st));
+                                  bar(kBQFull + st));
+                        if (!mbar_wait(bar(kBDoEmpty), (it & 1u) ^ 1u, abort_flag)) {
+                            report_timeout(p.status, 2, 13, it, 101);
+                            ok = false;
+                            break;
+                        }
+                        mbar_expect_tx(bar(kBDoFull), kTileBytes);
+                        tma_load_3d(sDO, &tm_do, 0, qt * 128, bq, bar(kBDoFull));
+                        tma_load_3d(sDO + kPanelBytes, &tm_do, 64, qt * 128, bq, bar(kBDoFull));
                     }
                 }
             }
@@ -269,49 +294,64 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 }
             };
             wait(kBKvFull, 0, 0, 200);
-            wait(kBQdoFull + 0, 0, 0, 201);
+            wait(kBQFull + 0, 0, 0, 201);
             if (ok) {
                 tc_fence_after();
                 mma_tile_kk(tST, sK, sQ(0), false);
                 umma_commit(bar(kBSFull));
-                mma_tile_kk(tDP, sV, sDO(0), false);
+            }
+            wait(kBDoFull, 0, 0, 202);
+            if (ok) {
+                tc_fence_after();
+                mma_tile_kk(tDP, sV, sDO, false);
                 umma_commit(bar(kBDpFull));
             }
             for (int it = 0; it < n_total && ok; ++it) {
                 const int st = it & 1;
                 const uint32_t ph = it & 1u;
+                if (it < 64) FBA_TRACE_REC(p.status, 1024 + it * 8 + 0);
                 wait(kBPReady, ph, it, 210);
                 if (!ok) break;
                 tc_fence_after();
-                mma_tile_tm(tDV, tST, tST + 64, sDO(st), it > 0);
+                if (it < 64) FBA_TRACE_REC(p.status, 1024 + it * 8 + 1);
+                mma_tile_tm(tDV, tST, tST + 64, sDO, it > 0);
+                umma_commit(bar(kBDoEmpty));          // dO(it) is free once dV (and the earlier dP) finished
                 if (it + 1 < n_total) {
-                    wait(kBQdoFull + (st ^ 1), ((it + 1) >> 1) & 1u, it, 211);
+                    wait(kBQFull + (st ^ 1), ((it + 1) >> 1) & 1u, it, 211);
                     if (!ok) break;
                     tc_fence_after();
                     mma_tile_kk(tST, sK, sQ(st ^ 1), false);
                     umma_commit(bar(kBSFull));
                 }
+                if (it < 64) FBA_TRACE_REC(p.status, 1024 + it * 8 + 2);
                 wait(kBDsReady, ph, it, 212);
                 if (!ok) break;
                 tc_fence_after();
-                mma_tile_km(tDK, sDS, sQ(st), it > 0);
-                mma_tile_mm(tDP, sDS, sK, false);
+                if (it < 64) FBA_TRACE_REC(p.status, 1024 + it * 8 + 3);
+                mma_tile_mm(tDP, sDS, sK, false);     // dQ first: its drain overlaps the dK GEMM
                 umma_commit(bar(kBDqFull));
-                umma_commit(bar(kBQdoEmpty + st));
+                mma_tile_km(tDK, sDS, sQ(st), it > 0);
+                umma_commit(bar(kBQEmpty + st));
+                if (it < 64) FBA_TRACE_REC(p.status, 1024 + it * 8 + 4);
                 if (it + 1 < n_total) {
+                    wait(kBDoFull, (it + 1) & 1u, it, 214);
                     wait(kBDqDrained, ph, it, 213);
                     if (!ok) break;
                     tc_fence_after();
-                    mma_tile_kk(tDP, sV, sDO(st ^ 1), false);
+                    if (it < 64) FBA_TRACE_REC(p.status, 1024 + it * 8 + 5);
+                    mma_tile_kk(tDP, sV, sDO, false);
+                    if (it < 64) FBA_TRACE_REC(p.status, 1024 + it * 8 + 7);
                     umma_commit(bar(kBDpFull));
+                    if (it < 64) FBA_TRACE_REC(p.status, 1024 + it * 8 + 6);
                 }
             }
             if (ok) umma_commit(bar(kBDkvDone));
         }
+      }
     } else if (warp >= 8) {
-        // ------------------------------------------------------------------ dQ drain + reduce
+        // ------------------------------------------------------------------ dQ drain
+        reg_inc<152>();
         const int quad = warp & 3;
-        const int row = quad * 32 + lane;  // query row inside the tile
         const uint32_t tdq = tDP + (static_cast<uint32_t>(quad * 32) << 16);
         int it = 0;
         bool ok = true;
@@ -329,27 +369,37 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     tc_fence_after();
-                    float* dst = p.dq_accum + ((bq * p.n_mtiles + (q0 + u)) * 32LL * 128 + row) * 4;
+                    if (warp == 8 && lane == 0 && it < 64) FBA_TRACE_REC(p.status, it * 8 + 4);
+                    float* dst = p.dq_accum + ((bq * p.n_mtiles + (q0 + u)) * 16LL + quad) * 1024;
+                    uint32_t v[128];
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc)
+                        tmem_ld32(tdq + 32u * cc, reinterpret_cast<uint32_t(&)[32]>(v[32 * cc]));
+                    tmem_wait_ld();
+                    tc_fence_before();
+                    mbar_arrive(bar(kBDqDrained));
+                    if (warp == 8 && lane == 0 && it < 64) FBA_TRACE_REC(p.status, it * 8 + 5);
+                    // One 16-byte reduction per lane and 4-column group; consecutive lanes hit
+                    // consecutive addresses (512 contiguous bytes per instruction).  The short
+                    // sleep spreads the 32 reductions of a tile over the iteration: issued back to
+                    // back they fill the memory-instruction queue that the MMA issue also uses.
 #pragma unroll
                     for (int cc = 0; cc < 4; ++cc) {
-                        uint32_t v[32];
-                        tmem_ld32(tdq + 32u * cc, v);
-                        tmem_wait_ld();
-                        if (cc == 3) {
-                            tc_fence_before();
-                            mbar_arrive(bar(kBDqDrained));
-                        }
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            red_add_v4(dst + (cc * 8 + j) * 512, __uint_as_float(v[4 * j]),
-                                       __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
-                                       __uint_as_float(v[4 * j + 3]));
+                        for (int j = 0; j < 8; ++j) {
+                            red_add_v4(dst + cc * 4096 + (j * 32 + lane) * 4, __uint_as_float(v[32 * cc + 4 * j]),
+                                       __uint_as_float(v[32 * cc + 4 * j + 1]), __uint_as_float(v[32 * cc + 4 * j + 2]),
+                                       __uint_as_float(v[32 * cc + 4 * j + 3]));
+                            __nanosleep(48);
+                        }
                     }
+                    if (warp == 8 && lane == 0 && it < 64) FBA_TRACE_REC(p.status, it * 8 + 6);
                 }
             }
         }
     } else {
         // ------------------------------------------------------------------ P^T / dS^T compute
+        reg_inc<152>();
         const int h = warp >> 2;           // query-column half of the tile
         const int quad = warp & 3;
         const int row = quad * 32 + lane;  // key row inside the tile == TMEM lane
@@ -365,15 +415,16 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 const uint32_t w = p.list.msk ? p.list.msk[lr * p.list.stride + e] : 0xffffu;
                 for (int u = 0; u < sub && ok; ++u, ++it) {
                     const int st = it & 1;
-                    const float2* ld = reinterpret_cast<const float2*>(base_ptr + kBwdSmemLD + st * 1024) + 64 * h;
+                    const float4* ld4 = reinterpret_cast<const float4*>(base_ptr + kBwdSmemLD + st * 1024) + 32 * h;
                     if (!mbar_wait(bar(kBSFull), it & 1u, abort_flag) ||
-                        !mbar_wait(bar(kBQdoFull + st), (it >> 1) & 1u, abort_flag)) {
+                        !mbar_wait(bar(kBQFull + st), (it >> 1) & 1u, abort_flag)) {
                         if (lane == 0) report_timeout(p.status, 2, static_cast<uint32_t>(warp), it, 400);
                         ok = false;
                     }
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     tc_fence_after();
+                    if (warp == 0 && lane == 0 && it < 64) FBA_TRACE_REC(p.status, it * 8 + 0);
                     float pr[64];
                     {
                         uint32_t s[64];
@@ -381,8 +432,11 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         tmem_ld32(tST + lane_base + 64u * h + 32u, reinterpret_cast<uint32_t(&)[32]>(s[32]));
                         tmem_wait_ld();
 #pragma unroll
-                        for (int j = 0; j < 64; ++j)
-                            pr[j] = ex2_approx(fmaf(__uint_as_float(s[j]), c, -ld[j].x));
+                        for (int j = 0; j < 32; ++j) {
+                            const float4 l2 = ld4[j];   // (lse2, delta) of columns 2j and 2j+1
+                            pr[2 * j] = ex2_approx(fmaf(__uint_as_float(s[2 * j]), c, -l2.x));
+                            pr[2 * j + 1] = ex2_approx(fmaf(__uint_as_float(s[2 * j + 1]), c, -l2.z));
+                        }
                     }
                     if (w != 0xffffu) {
 #pragma unroll
@@ -399,6 +453,7 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     tmem_wait_st();
                     tc_fence_before();
                     mbar_arrive(bar(kBPReady));
+                    if (warp == 0 && lane == 0 && it < 64) FBA_TRACE_REC(p.status, it * 8 + 1);
 
                     if (!mbar_wait(bar(kBDpFull), it & 1u, abort_flag)) {
                         if (lane == 0) report_timeout(p.status, 2, static_cast<uint32_t>(warp), it, 401);
@@ -407,31 +462,31 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     tc_fence_after();
+                    if (warp == 0 && lane == 0 && it < 64) FBA_TRACE_REC(p.status, it * 8 + 2);
                     uint8_t* ds_row = base_ptr + kBwdSmemDS + static_cast<uint32_t>(h) * kPanelBytes +
                                       static_cast<uint32_t>(row) * 128u;
+                    uint32_t dp[64];
+                    tmem_ld32(tDP + lane_base + 64u * h, reinterpret_cast<uint32_t(&)[32]>(dp[0]));
+                    tmem_ld32(tDP + lane_base + 64u * h + 32u, reinterpret_cast<uint32_t(&)[32]>(dp[32]));
+                    tmem_wait_ld();
 #pragma unroll
-                    for (int cc = 0; cc < 2; ++cc) {
-                        uint32_t dp[32];
-                        tmem_ld32(tDP + lane_base + 64u * h + 32u * cc, dp);
-                        tmem_wait_ld();
+                    for (int q8 = 0; q8 < 8; ++q8) {
+                        uint32_t wds[4];
 #pragma unroll
-                        for (int q4 = 0; q4 < 4; ++q4) {
-                            uint32_t wds[4];
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const int col = 32 * cc + 8 * q4 + 2 * j;
-                                const float d0 = pr[col] * (__uint_as_float(dp[8 * q4 + 2 * j]) - ld[col].y) * kSoftmaxScale;
-                                const float d1 = pr[col + 1] * (__uint_as_float(dp[8 * q4 + 2 * j + 1]) - ld[col + 1].y) * kSoftmaxScale;
-                                wds[j] = pack_bf16x2(d0, d1);
-                            }
-                            const int chunk = cc * 4 + q4;  // 16-byte chunk 0..7 of this 128-byte row
-                            *reinterpret_cast<uint4*>(ds_row + (static_cast<uint32_t>(chunk ^ (row & 7)) << 4)) =
-                                make_uint4(wds[0], wds[1], wds[2], wds[3]);
+                        for (int j = 0; j < 4; ++j) {
+                            const int col = 8 * q8 + 2 * j;
+                            const float4 l2 = ld4[col >> 1];
+                            const float d0 = pr[col] * (__uint_as_float(dp[col]) - l2.y) * kSoftmaxScale;
+                            const float d1 = pr[col + 1] * (__uint_as_float(dp[col + 1]) - l2.w) * kSoftmaxScale;
+                            wds[j] = pack_bf16x2(d0, d1);
                         }
+                        *reinterpret_cast<uint4*>(ds_row + (static_cast<uint32_t>(q8 ^ (row & 7)) << 4)) =
+                            make_uint4(wds[0], wds[1], wds[2], wds[3]);
                     }
                     fence_proxy_async_smem();
                     tc_fence_before();
                     mbar_arrive(bar(kBDsReady));
+                    if (warp == 0 && lane == 0 && it < 64) FBA_TRACE_REC(p.status, it * 8 + 3);
                 }
             }
         }
@@ -444,7 +499,7 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             }
             ok = __all_sync(0xffffffffu, ok);
         }
-        const uint32_t stage_off = h == 0 ? kBwdSmemQ : kBwdSmemDO;
+        const uint32_t stage_off = h == 0 ? kBwdSmemQ : kBwdSmemQ + kTileBytes;
         if (ok) {
             tc_fence_after();
             const uint32_t tsrc = (h == 0 ? tDV : tDK) + lane_base;

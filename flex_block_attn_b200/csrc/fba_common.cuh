@@ -28,6 +28,20 @@ inline ListDev to_dev(const fba_list_t& l) {
     return ListDev{l.idx, l.cnt, l.msk, l.stride, l.rows_per_bh, l.bh_stride, l.rows_div, l.sub};
 }
 
+// Optional timeline probe for tuning (compiled out unless -DFBA_TRACE): CTA (0,0) stores SM clock
+// stamps as 64-bit words after the 8 status words, so the status buffer must then be large.
+#ifdef FBA_TRACE
+#define FBA_TRACE_REC(status, idx)                                                              \
+    do {                                                                                        \
+        if (blockIdx.x == 0 && blockIdx.y == 0)                                                 \
+            reinterpret_cast<unsigned long long*>(status)[8 + (idx)] = clock64();               \
+    } while (0)
+#else
+#define FBA_TRACE_REC(status, idx) \
+    do {                           \
+    } while (0)
+#endif
+
 // Record the first place a bounded wait gave up.
 __device__ __forceinline__ void report_timeout(uint32_t* status, uint32_t kernel, uint32_t role,
                                                uint32_t iter, uint32_t tag) {

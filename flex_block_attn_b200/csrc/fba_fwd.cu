@@ -14,7 +14,10 @@
 //   * one thread streams only the listed K / V tiles through a 5-stage shared-memory ring with
 //     TMA + mbarrier; the list comes from the compaction kernel, not from scanning the mask;
 //   * rescaling of O is lazy (only when the running row max grew by more than 2^8), done by the
-//     softmax warps between two MMAs of their tile.
+//     softmax warps between two MMAs of their tile;
+//   * P reaches the tensor core in two halves (keys 0-63, then 64-127) so O += P V starts while the
+//     second half of the exponentials is still being computed, and a fixed fraction of the
+//     exponentials is evaluated by a polynomial on the FMA pipe to unload the special-function unit.
 //
 // If both query tiles map to the same list row they share every K / V stage; otherwise each tile
 // streams its own list ("split" mode) in a fixed interleaving that loader and issuer both follow.
@@ -22,12 +25,19 @@
 
 namespace fba {
 
-constexpr int kFwdThreads = 320;  // warps 0-3 softmax A, 4-7 softmax B, 8 MMA issue, 9 TMA
+constexpr int kFwdThreads = 384;  // warpgroup 0: softmax A, 1: softmax B, 2: {MMA issue, TMA, 2 idle warps}
 constexpr int kFwdStages = 5;
 constexpr uint32_t kFwdSmemQ = 0;
 constexpr uint32_t kFwdSmemRing = 2 * kTileBytes;
 constexpr uint32_t kFwdSmemBars = kFwdSmemRing + kFwdStages * kTileBytes;
 constexpr uint32_t kFwdSmemBytes = kFwdSmemBars + 256 + 1024;  // + alignment slack
+
+// Of every 16 pairs of exponentials, this many are evaluated by ex2_poly2 on the FMA pipe and the
+// rest by the special-function unit (16 ex2 / clk / SM, which would otherwise cap the kernel at
+// the tensor core's own time for a 128-wide head).
+#ifndef FBA_FWD_POLY_PAIRS
+#define FBA_FWD_POLY_PAIRS 0
+#endif
 
 struct FwdParams {
     ListDev list;
@@ -42,10 +52,23 @@ enum FwdBar : uint32_t {
     kBarRingFull = 2,                      // kFwdStages
     kBarRingEmpty = 2 + kFwdStages,        // kFwdStages
     kBarSFull = 2 + 2 * kFwdStages,        // 2
-    kBarPReady = 4 + 2 * kFwdStages,       // 2
-    kBarODone = 6 + 2 * kFwdStages,        // 2
-    kBarCount = 8 + 2 * kFwdStages
+    kBarPLo = 4 + 2 * kFwdStages,          // 2: P columns 0-63 (keys 0-63 of the tile) are in TMEM
+    kBarPHi = 6 + 2 * kFwdStages,          // 2: keys 64-127
+    kBarODone = 8 + 2 * kFwdStages,        // 2
+    kBarCount = 10 + 2 * kFwdStages
 };
+
+// One half (4 k-steps = 64 keys) of O += P V.
+__device__ __forceinline__ void mma_pv_half(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_smem, int half,
+                                            bool accumulate) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int kk = half * 4 + k;
+        umma_ts(d_tmem, p_tmem + static_cast<uint32_t>(kk) * 8u,
+                umma_desc_mnmajor(v_smem + static_cast<uint32_t>(kk) * 2048u), kIdescKM,
+                (accumulate || kk > 0) ? 1u : 0u);
+    }
+}
 
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -68,18 +91,14 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const int bhk = (bh / p.Hq) * p.Hkv + (bh % p.Hq) / hr;
 
     // Per-tile list rows and lengths (identical in every thread).
-    int mt[2] = {2 * pair, 2 * pair + 1};
-    long long lrow[2];
-    int n[2];
-#pragma unroll
-    for (int t = 0; t < 2; ++t) {
-        const bool valid = mt[t] < p.n_mtiles;
-        lrow[t] = static_cast<long long>(bh) * p.list.bh_stride + (valid ? mt[t] / p.list.rows_div : 0);
-        n[t] = valid ? p.list.cnt[lrow[t]] * p.list.sub : 0;
-    }
-    const bool tile1_valid = mt[1] < p.n_mtiles;
-    const bool shared_mode = tile1_valid && lrow[0] == lrow[1];
+    const int mt0 = 2 * pair, mt1 = 2 * pair + 1;
+    const bool tile1_valid = mt1 < p.n_mtiles;
+    const long long lrow0 = static_cast<long long>(bh) * p.list.bh_stride + mt0 / p.list.rows_div;
+    const long long lrow1 = static_cast<long long>(bh) * p.list.bh_stride + (tile1_valid ? mt1 / p.list.rows_div : 0);
     const int sub = p.list.sub;
+    const int n0 = p.list.cnt[lrow0] * sub;
+    const int n1 = tile1_valid ? p.list.cnt[lrow1] * sub : 0;
+    const bool shared_mode = tile1_valid && lrow0 == lrow1;
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -91,7 +110,8 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(bar(kBarSFull + t), 1);
-            mbar_init(bar(kBarPReady + t), 128);
+            mbar_init(bar(kBarPLo + t), 128);
+            mbar_init(bar(kBarPHi + t), 128);
             mbar_init(bar(kBarODone + t), 1);
         }
         mbar_fence_init();
@@ -110,131 +130,159 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t sQ[2] = {base + kFwdSmemQ, base + kFwdSmemQ + kTileBytes};
+    const uint32_t sQ0 = base + kFwdSmemQ, sQ1 = base + kFwdSmemQ + kTileBytes;
     auto ring = [&](int s) { return base + kFwdSmemRing + static_cast<uint32_t>(s) * kTileBytes; };
     auto kv_tile_of = [&](int t, int i) {
         const int e = i / sub;
-        return p.list.idx[lrow[t] * p.list.stride + e] * sub + (i - e * sub);
+        return p.list.idx[(t ? lrow1 : lrow0) * p.list.stride + e] * sub + (i - e * sub);
     };
 
-    if (warp == 9) {
-        // ------------------------------------------------------------------ TMA loader
-        if (lane == 0) {
-            bool ok = true;
-            uint32_t prod = 0;
-            for (int t = 0; t < 2; ++t) {
-                if (n[t] > 0) {
-                    mbar_expect_tx(bar(kBarQFull + t), kTileBytes);
-                    tma_load_3d(sQ[t], &tm_q, 0, mt[t] * 128, bh, bar(kBarQFull + t));
-                    tma_load_3d(sQ[t] + kPanelBytes, &tm_q, 64, mt[t] * 128, bh, bar(kBarQFull + t));
+    if (warp >= 8) {
+        // Register pool of the CTA = 384 threads x 168 at launch = 3 x 128 x 168.  The budgets set
+        // below must not add up to more than that (200 + 200 + 96 <= 504), or the increase would
+        // wait for registers that are never released.
+        reg_dec<96>();
+        if (warp == 9) {
+            // -------------------------------------------------------------- TMA loader
+            if (lane == 0) {
+                bool ok = true;
+                uint32_t prod = 0;
+                if (n0 > 0) {
+                    mbar_expect_tx(bar(kBarQFull + 0), kTileBytes);
+                    tma_load_3d(sQ0, &tm_q, 0, mt0 * 128, bh, bar(kBarQFull + 0));
+                    tma_load_3d(sQ0 + kPanelBytes, &tm_q, 64, mt0 * 128, bh, bar(kBarQFull + 0));
                 }
-            }
-            auto load = [&](const CUtensorMap* tm, int kv_tile, uint32_t tag) {
-                if (!ok) return;
-                const int s = prod % kFwdStages;
-                const uint32_t parity = ((prod / kFwdStages) & 1u) ^ 1u;
-                if (!mbar_wait(bar(kBarRingEmpty + s), parity, abort_flag)) {
-                    report_timeout(p.status, 1, 9, prod, tag);
-                    ok = false;
-                    return;
+                if (n1 > 0) {
+                    mbar_expect_tx(bar(kBarQFull + 1), kTileBytes);
+                    tma_load_3d(sQ1, &tm_q, 0, mt1 * 128, bh, bar(kBarQFull + 1));
+                    tma_load_3d(sQ1 + kPanelBytes, &tm_q, 64, mt1 * 128, bh, bar(kBarQFull + 1));
                 }
-                mbar_expect_tx(bar(kBarRingFull + s), kTileBytes);
-                tma_load_3d(ring(s), tm, 0, kv_tile * 128, bhk, bar(kBarRingFull + s));
-                tma_load_3d(ring(s) + kPanelBytes, tm, 64, kv_tile * 128, bhk, bar(kBarRingFull + s));
-                ++prod;
-            };
-            const int ln[2] = {n[0], shared_mode ? 0 : n[1]};
-            const int nmax = ln[0] > ln[1] ? ln[0] : ln[1];
-            for (int t = 0; t < 2; ++t)
-                if (ln[t] > 0) load(&tm_k, kv_tile_of(t, 0), 100 + t);
-            for (int i = 0; i < nmax && ok; ++i) {
-                for (int t = 0; t < 2; ++t) {
-                    if (i < ln[t]) {
-                        load(&tm_v, kv_tile_of(t, i), 200 + t);
-                        if (i + 1 < ln[t]) load(&tm_k, kv_tile_of(t, i + 1), 100 + t);
+                auto load = [&](const CUtensorMap* tm, int kv_tile, uint32_t tag) {
+                    if (!ok) return;
+                    const int s = prod % kFwdStages;
+                    const uint32_t parity = ((prod / kFwdStages) & 1u) ^ 1u;
+                    if (!mbar_wait(bar(kBarRingEmpty + s), parity, abort_flag)) {
+                        report_timeout(p.status, 1, 9, prod, tag);
+                        ok = false;
+                        return;
+                    }
+                    mbar_expect_tx(bar(kBarRingFull + s), kTileBytes);
+                    tma_load_3d(ring(s), tm, 0, kv_tile * 128, bhk, bar(kBarRingFull + s));
+                    tma_load_3d(ring(s) + kPanelBytes, tm, 64, kv_tile * 128, bhk, bar(kBarRingFull + s));
+                    ++prod;
+                };
+                const int ln[2] = {n0, shared_mode ? 0 : n1};
+                const int nmax = ln[0] > ln[1] ? ln[0] : ln[1];
+                for (int t = 0; t < 2; ++t)
+                    if (ln[t] > 0) load(&tm_k, kv_tile_of(t, 0), 100 + t);
+                for (int i = 0; i < nmax && ok; ++i) {
+                    for (int t = 0; t < 2; ++t) {
+                        if (i < ln[t]) {
+                            load(&tm_v, kv_tile_of(t, i), 200 + t);
+                            if (i + 1 < ln[t]) load(&tm_k, kv_tile_of(t, i + 1), 100 + t);
+                        }
                     }
                 }
             }
-        }
-    } else if (warp == 8) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            bool ok = true;
-            uint32_t cons = 0;
-            const uint32_t tS[2] = {tmem + 0, tmem + 128};
-            const uint32_t tO[2] = {tmem + 256, tmem + 384};
-            auto acquire = [&](uint32_t tag) -> int {
-                const int s = cons % kFwdStages;
-                if (!mbar_wait(bar(kBarRingFull + s), (cons / kFwdStages) & 1u, abort_flag)) {
-                    report_timeout(p.status, 1, 8, cons, tag);
-                    ok = false;
-                }
-                ++cons;
-                return s;
-            };
-            int slot_k[2] = {0, 0}, slot_v[2] = {0, 0};
-            // Prologue: S(0) of both tiles.
-            for (int t = 0; t < 2 && ok; ++t) {
-                if (n[t] == 0) continue;
-                if (!mbar_wait(bar(kBarQFull + t), 0, abort_flag)) {
-                    report_timeout(p.status, 1, 8, 0, 300 + t);
-                    ok = false;
-                    break;
-                }
-                const bool reuse = shared_mode && t == 1;
-                slot_k[t] = reuse ? slot_k[0] : acquire(310 + t);
-                if (!ok) break;
-                tc_fence_after();
-                mma_tile_kk(tS[t], sQ[t], ring(slot_k[t]), false);
-                umma_commit(bar(kBarSFull + t));
-                if (!shared_mode || t == 1) umma_commit(bar(kBarRingEmpty + slot_k[t]));
-            }
-            const int nmax = n[0] > n[1] ? n[0] : n[1];
-            for (int i = 0; i < nmax && ok; ++i) {
+        } else if (warp == 8) {
+            // -------------------------------------------------------------- MMA issuer
+            if (lane == 0) {
+                bool ok = true;
+                uint32_t cons = 0;
+                const int n[2] = {n0, n1};
+                const uint32_t sQ[2] = {sQ0, sQ1};
+                const uint32_t tS[2] = {tmem + 0, tmem + 128};
+                const uint32_t tO[2] = {tmem + 256, tmem + 384};
+                auto acquire = [&](uint32_t tag) -> int {
+                    const int s = cons % kFwdStages;
+                    if (!mbar_wait(bar(kBarRingFull + s), (cons / kFwdStages) & 1u, abort_flag)) {
+                        report_timeout(p.status, 1, 8, cons, tag);
+                        ok = false;
+                    }
+                    ++cons;
+                    return s;
+                };
+                int slot_k[2] = {0, 0}, slot_v[2] = {0, 0};
+                // Prologue: S(0) of both tiles.
                 for (int t = 0; t < 2 && ok; ++t) {
-                    if (i >= n[t]) continue;
-                    const bool reuse = shared_mode && t == 1;
-                    const bool release = !shared_mode || t == 1;
-                    if (!mbar_wait(bar(kBarPReady + t), i & 1u, abort_flag)) {
-                        report_timeout(p.status, 1, 8, i, 320 + t);
+                    if (n[t] == 0) continue;
+                    if (!mbar_wait(bar(kBarQFull + t), 0, abort_flag)) {
+                        report_timeout(p.status, 1, 8, 0, 300 + t);
                         ok = false;
                         break;
                     }
-                    slot_v[t] = reuse ? slot_v[0] : acquire(330 + t);
+                    const bool reuse = shared_mode && t == 1;
+                    slot_k[t] = reuse ? slot_k[0] : acquire(310 + t);
                     if (!ok) break;
                     tc_fence_after();
-                    mma_tile_tm(tO[t], tS[t], tS[t] + 32, ring(slot_v[t]), i > 0);
-                    if (release) umma_commit(bar(kBarRingEmpty + slot_v[t]));
-                    if (i + 1 < n[t]) {
-                        slot_k[t] = reuse ? slot_k[0] : acquire(340 + t);
+                    mma_tile_kk(tS[t], sQ[t], ring(slot_k[t]), false);
+                    umma_commit(bar(kBarSFull + t));
+                    if (!shared_mode || t == 1) umma_commit(bar(kBarRingEmpty + slot_k[t]));
+                }
+                const int nmax = n[0] > n[1] ? n[0] : n[1];
+                for (int i = 0; i < nmax && ok; ++i) {
+                    for (int t = 0; t < 2 && ok; ++t) {
+                        if (i >= n[t]) continue;
+                        const bool reuse = shared_mode && t == 1;
+                        const bool release = !shared_mode || t == 1;
+                        if (i < 64) FBA_TRACE_REC(p.status, 1024 + i * 8 + t * 4 + 0);
+                        slot_v[t] = reuse ? slot_v[0] : acquire(330 + t);
                         if (!ok) break;
+                        if (!mbar_wait(bar(kBarPLo + t), i & 1u, abort_flag)) {
+                            report_timeout(p.status, 1, 8, i, 320 + t);
+                            ok = false;
+                            break;
+                        }
                         tc_fence_after();
-                        mma_tile_kk(tS[t], sQ[t], ring(slot_k[t]), false);
-                        umma_commit(bar(kBarSFull + t));
-                        if (release) umma_commit(bar(kBarRingEmpty + slot_k[t]));
-                    } else {
-                        umma_commit(bar(kBarODone + t));
+                        if (i < 64) FBA_TRACE_REC(p.status, 1024 + i * 8 + t * 4 + 1);
+                        mma_pv_half(tO[t], tS[t], ring(slot_v[t]), 0, i > 0);
+                        if (!mbar_wait(bar(kBarPHi + t), i & 1u, abort_flag)) {
+                            report_timeout(p.status, 1, 8, i, 325 + t);
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        mma_pv_half(tO[t], tS[t], ring(slot_v[t]), 1, true);
+                        if (release) umma_commit(bar(kBarRingEmpty + slot_v[t]));
+                        if (i + 1 < n[t]) {
+                            slot_k[t] = reuse ? slot_k[0] : acquire(340 + t);
+                            if (!ok) break;
+                            tc_fence_after();
+                            mma_tile_kk(tS[t], sQ[t], ring(slot_k[t]), false);
+                            umma_commit(bar(kBarSFull + t));
+                            if (release) umma_commit(bar(kBarRingEmpty + slot_k[t]));
+                        } else {
+                            umma_commit(bar(kBarODone + t));
+                        }
+                        if (i < 64) FBA_TRACE_REC(p.status, 1024 + i * 8 + t * 4 + 2);
                     }
                 }
             }
         }
     } else {
         // ------------------------------------------------------------------ softmax + epilogue
+        reg_inc<200>();
         const int t = warp >> 2;                       // 0: tile A, 1: tile B
         const int row = (warp & 3) * 32 + lane;        // row inside the tile == TMEM lane
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t tS = tmem + lane_base + static_cast<uint32_t>(t) * 128u;
         const uint32_t tO = tmem + lane_base + 256u + static_cast<uint32_t>(t) * 128u;
-        const bool tile_valid = mt[t] < p.n_mtiles;
+        const int mt = t ? mt1 : mt0;
+        const int nt = t ? n1 : n0;
+        const long long lrow = t ? lrow1 : lrow0;
+        const uint32_t sQt = t ? sQ1 : sQ0;
+        const bool tile_valid = mt < p.n_mtiles;
         const float c = kSoftmaxScale * kLog2e;
+        const float2 c2 = make_float2(c, c);
         const int g = row >> 4;
+        const bool tracer = (warp & 3) == 0 && lane == 0;
 
         float off = 0.f;        // exponent offset (scaled-by-c row max the exponentials refer to)
         bool have_off = false;  // false until the row has seen a finite score
-        float l = 0.f;
+        float2 l2a = make_float2(0.f, 0.f), l2b = make_float2(0.f, 0.f);
         bool ok = true;
 
-        for (int i = 0; i < n[t] && ok; ++i) {
+        for (int i = 0; i < nt && ok; ++i) {
             if (!mbar_wait(bar(kBarSFull + t), i & 1u, abort_flag)) {
                 if (lane == 0) report_timeout(p.status, 1, static_cast<uint32_t>(warp), i, 400 + t);
                 ok = false;
@@ -242,14 +290,16 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
+            if (tracer && i < 64) FBA_TRACE_REC(p.status, i * 8 + t * 4 + 0);
             uint32_t u[128];
 #pragma unroll
             for (int cc = 0; cc < 4; ++cc)
                 tmem_ld32(tS + 32u * cc, reinterpret_cast<uint32_t(&)[32]>(u[32 * cc]));
             tmem_wait_ld();
+            if (tracer && i < 64) FBA_TRACE_REC(p.status, i * 8 + t * 4 + 1);
 
             if (p.list.msk != nullptr) {
-                const uint32_t w = p.list.msk[lrow[t] * p.list.stride + i / sub];
+                const uint32_t w = p.list.msk[lrow * p.list.stride + i / sub];
                 if (w != 0xffffu) {
                     const bool keep0 = (w >> g) & 1u, keep1 = (w >> (8 + g)) & 1u;
 #pragma unroll
@@ -259,9 +309,16 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     }
                 }
             }
-            float mx = -INFINITY;
+            float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-            for (int j = 0; j < 128; ++j) mx = fmaxf(mx, __uint_as_float(u[j]));
+            for (int j = 0; j < 128; j += 8) {
+                m0 = max3(m0, __uint_as_float(u[j + 0]), __uint_as_float(u[j + 1]));
+                m1 = max3(m1, __uint_as_float(u[j + 2]), __uint_as_float(u[j + 3]));
+                m2 = max3(m2, __uint_as_float(u[j + 4]), __uint_as_float(u[j + 5]));
+                m3 = max3(m3, __uint_as_float(u[j + 6]), __uint_as_float(u[j + 7]));
+            }
+            const float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+            if (tracer && i < 64) FBA_TRACE_REC(p.status, i * 8 + t * 4 + 2);
 
             float alpha = 1.f;
             const float cand = mx * c;
@@ -276,7 +333,7 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             }
             if (i > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
                 // Rescale this warp's 32 rows of O.  The previous P V of this tile has completed
-                // (the commit that released S covers it) and the next one waits for p_ready.
+                // (the commit that released S covers it) and the next one waits for the P barriers.
 #pragma unroll
                 for (int cc = 0; cc < 4; ++cc) {
                     uint32_t v[32];
@@ -287,34 +344,46 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     tmem_st32(tO + 32u * cc, v);
                 }
             }
-            l *= alpha;
+            l2a.x *= alpha;
+            l2a.y *= alpha;
+            l2b.x *= alpha;
+            l2b.y *= alpha;
             const float neg_off = have_off ? -off : 0.f;
+            const float2 noff2 = make_float2(neg_off, neg_off);
 #pragma unroll
-            for (int cc = 0; cc < 8; ++cc) {
+            for (int cc = 0; cc < 4; ++cc) {
                 uint32_t pk[16];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const float p0 = ex2_approx(fmaf(__uint_as_float(u[16 * cc + 2 * j]), c, neg_off));
-                    const float p1 = ex2_approx(fmaf(__uint_as_float(u[16 * cc + 2 * j + 1]), c, neg_off));
-                    l += p0 + p1;
-                    pk[j] = pack_bf16x2(p0, p1);
+                for (int j = 0; j < 16; ++j) {
+                    const float2 x = fma2(make_float2(__uint_as_float(u[32 * cc + 2 * j]), __uint_as_float(u[32 * cc + 2 * j + 1])),
+                                          c2, noff2);
+                    float2 e;
+                    if (j < FBA_FWD_POLY_PAIRS) {
+                        e = ex2_poly2(x);
+                    } else {
+                        e.x = ex2_approx(x.x);
+                        e.y = ex2_approx(x.y);
+                    }
+                    if (j & 1) l2b = add2(l2b, e); else l2a = add2(l2a, e);
+                    pk[j] = pack_bf16x2(e.x, e.y);
                 }
-                // 16 scores -> 8 packed columns
-                asm volatile(
-                    "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(
-                        tS + 8u * cc),
-                    "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]), "r"(pk[6]),
-                    "r"(pk[7])
-                    : "memory");
+                tmem_st16(tS + 16u * cc, pk);
+                if (cc == 1) {
+                    tmem_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(bar(kBarPLo + t));
+                }
             }
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(bar(kBarPReady + t));
+            mbar_arrive(bar(kBarPHi + t));
+            if (tracer && i < 64) FBA_TRACE_REC(p.status, i * 8 + t * 4 + 3);
         }
+        const float l = (l2a.x + l2a.y) + (l2b.x + l2b.y);
 
         // Epilogue: O / l -> bf16 -> swizzled staging in this tile's Q buffer -> TMA store.
         if (tile_valid) {
-            if (n[t] > 0 && ok) {
+            if (nt > 0 && ok) {
                 if (!mbar_wait(bar(kBarODone + t), 0, abort_flag)) {
                     if (lane == 0) report_timeout(p.status, 1, static_cast<uint32_t>(warp), 0, 500 + t);
                     ok = false;
@@ -328,7 +397,7 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
                 for (int cc = 0; cc < 4; ++cc) {
                     uint32_t v[32];
-                    if (n[t] > 0) {
+                    if (nt > 0) {
                         tmem_ld32(tO + 32u * cc, v);
                         tmem_wait_ld();
                     } else {
@@ -349,7 +418,7 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         *reinterpret_cast<uint4*>(stage + o) = w;
                     }
                 }
-                const int grow = mt[t] * 128 + row;
+                const int grow = mt * 128 + row;
                 if (grow < p.Sq)
                     p.lse[static_cast<long long>(bh) * p.Sq + grow] =
                         l > 0.f ? (off + lg2_approx(l)) * kLn2 : -INFINITY;
@@ -357,8 +426,8 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             }
             named_bar_sync(1 + t, 128);
             if (ok && (warp & 3) == 0 && lane == 0) {
-                tma_store_3d(&tm_o, 0, mt[t] * 128, bh, sQ[t]);
-                tma_store_3d(&tm_o, 64, mt[t] * 128, bh, sQ[t] + kPanelBytes);
+                tma_store_3d(&tm_o, 0, mt * 128, bh, sQt);
+                tma_store_3d(&tm_o, 64, mt * 128, bh, sQt + kPanelBytes);
                 tma_commit_group();
                 tma_wait_group0();
             }

@@ -43,6 +43,68 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return r;
 }
 
+// 3-input max (one instruction on sm_100).
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// Packed fp32 pairs (sm_100 executes these as one instruction on a 64-bit register pair).
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "mul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+// 2^x for a pair, computed on the FMA pipe instead of the (4x narrower) special-function unit:
+// x = floor(x) + f, 2^f by a degree-3 polynomial on [0,1) (max relative error 8.7e-5, far below
+// bf16 rounding of the result), 2^floor(x) by adding to the exponent field.  Inputs below -126
+// (including -inf, i.e. masked scores) give exactly 0, like ex2.approx.ftz; x must be below 128.
+__device__ __forceinline__ float2 ex2_poly2(float2 x) {
+    const bool zx = x.x < -126.f, zy = x.y < -126.f;
+    x.x = fmaxf(x.x, -126.f);
+    x.y = fmaxf(x.y, -126.f);
+    const float magic = 12582912.f;  // 1.5 * 2^23: adding it leaves round-down(x) in the low mantissa bits
+    float2 t;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\t"
+        "add.rm.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(t.x), "=f"(t.y)
+        : "f"(x.x), "f"(x.y), "f"(magic));
+    const float2 fl = add2(t, make_float2(-magic, -magic));
+    const float2 f = add2(x, make_float2(-fl.x, -fl.y));
+    float2 p = fma2(f, make_float2(0.07705805f, 0.07705805f), make_float2(0.22764558f, 0.22764558f));
+    p = fma2(p, f, make_float2(0.69512289f, 0.69512289f));
+    p = fma2(p, f, make_float2(1.f, 1.f));
+    float2 r;
+    r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
+    r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
+    if (zx) r.x = 0.f;
+    if (zy) r.y = 0.f;
+    return r;
+}
+
 // ------------------------------------------------------------------------------------------
 // mbarrier
 // ------------------------------------------------------------------------------------------
@@ -83,6 +145,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     uint32_t it = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
+#ifdef FBA_SPIN_SLEEP_NS
+        __nanosleep(FBA_SPIN_SLEEP_NS);
+#endif
         if (((++it) & 63u) == 0u) {
             if (*abort_flag) return false;
             if (clock64() - t0 > kWaitLimitCycles) {
@@ -196,6 +261,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]),
         "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
+}
+template <int N>
+__device__ __forceinline__ void reg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile(
