@@ -1,7 +1,7 @@
 // Block-sparse attention backward for sm_100a.
 //
 // Three kernels, in stream order:
-//   1. bwd_prep_kernel      (lse2, delta)[row] = (LSE * log2 e, sum_d dO * O); the counterpart of
+//   1. bwd_prep_kernel      per row (-LSE * log2 e, -sum_d dO * O / sqrt(128)); the counterpart of
 //                           the reference's bwd_attend_prep_ker (flex_block_attn_h100.cu:339-389).
 //                           HBM-bound, one pass over O and dO.
 //   2. fba_bwd_kernel       key-major main kernel, the counterpart of bwd_attend_ker (.cu:572-802).
@@ -23,11 +23,10 @@
 //
 // Warp roles of the main kernel (448 threads): warps 0-7 compute P^T and dS^T (thread = key row;
 // warps 0-3 take query columns 0-63 of the tile, warps 4-7 columns 64-127), warps 8-11 drain dQ
-// from TMEM, warp 12 issues every MMA, warp 13 drives TMA.
+// from TMEM, warps 12 and 14 issue the MMAs (two independent chains), warp 13 drives TMA.
 //
 // Shared memory: K, V resident (64 KiB); Q double-buffered with its (lse2, delta) rows (64 + 2 KiB);
-// dO single-buffered (32 KiB; it is reloaded between dV of one query tile and dP^T of the next);
-// dS^T (32 KiB).
+// dO double-buffered (64 KiB); dS^T (32 KiB).
 #include "fba_common.cuh"
 
 namespace fba {
@@ -36,27 +35,35 @@ constexpr int kBwdThreads = 512;  // 4 warpgroups: compute, compute, dQ drain, {
 constexpr uint32_t kBwdSmemK = 0;
 constexpr uint32_t kBwdSmemV = 1 * kTileBytes;
 constexpr uint32_t kBwdSmemQ = 2 * kTileBytes;    // 2 stages
-constexpr uint32_t kBwdSmemDO = 4 * kTileBytes;   // 1 stage
-constexpr uint32_t kBwdSmemDS = 5 * kTileBytes;
+constexpr uint32_t kBwdSmemDO = 4 * kTileBytes;   // 2 stages
+constexpr uint32_t kBwdSmemDS = 6 * kTileBytes;
 constexpr uint32_t kBwdSmemLD = 7 * kTileBytes;     // 2 stages x 128 x (lse2, delta)
 constexpr uint32_t kBwdSmemBars = kBwdSmemLD + 2 * 1024;
-constexpr uint32_t kBwdSmemBytes = kBwdSmemBars + 128;
+
 
 enum BwdBar : uint32_t {
     kBKvFull = 0,
     kBQFull = 1,      // 2
     kBQEmpty = 3,     // 2
-    kBDoFull = 5,
-    kBDoEmpty = 6,
-    kBSFull = 7,
-    kBPReady = 8,
-    kBDpFull = 9,
-    kBDsReady = 10,
-    kBDqFull = 11,
-    kBDqDrained = 12,
-    kBDkvDone = 13,
-    kBCount = 14
+    kBDoFull = 5,     // 2
+    kBDoEmpty = 7,    // 2
+    kBSFull = 9,
+    kBPReady = 10,
+    kBDpFull = 11,
+    kBDsReady = 12,
+    kBDqFull = 13,
+    kBDqDrained = 14,
+    kBDkvDone = 15,
+    kBCount = 16
 };
+// barriers, then the TMEM base slot and the abort flag
+constexpr uint32_t kBwdSmemBytes = kBwdSmemBars + 8 * kBCount + 16;
+static_assert(kBwdSmemBytes <= 232448, "exceeds the 227 KiB shared memory of an sm_100 CTA");
+
+// Pause between two of the 32 vector reductions a drain thread issues per query tile.
+#ifndef FBA_RED_SLEEP_NS
+#define FBA_RED_SLEEP_NS 32
+#endif
 
 struct BwdParams {
     ListDev list;          // key-major: rows = key tiles / rows_div, entries = query tiles / sub
@@ -77,7 +84,10 @@ __global__ void __launch_bounds__(256) bwd_prep_kernel(const __nv_bfloat16* __re
     const int lane = threadIdx.x & 31;
     const long long bh = w / rows_pad;
     const int r = static_cast<int>(w % rows_pad);
-    float2 out = make_float2(INFINITY, 0.f);
+    // Output layout, per pair of consecutive rows (2j, 2j+1): (-lse2[2j], -lse2[2j+1],
+    // -delta[2j] / sqrt(128), -delta[2j+1] / sqrt(128)), so the main kernel reads one 16-byte word
+    // per column pair and feeds it straight into packed fused multiply-adds.
+    float neg_lse2 = -INFINITY, neg_delta_s = 0.f;
     if (r < Sq) {
         const long long row = bh * Sq + r;
         const uint2 a = reinterpret_cast<const uint2*>(o + row * 128)[lane];
@@ -95,10 +105,16 @@ __global__ void __launch_bounds__(256) bwd_prep_kernel(const __nv_bfloat16* __re
 #pragma unroll
         for (int m = 16; m > 0; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
         const float l = lse[row];
-        // A row that attended to nothing has LSE = -inf; +inf here makes every P of it exactly 0.
-        out = make_float2(l == -INFINITY ? INFINITY : l * kLog2e, s);
+        // A row that attended to nothing has LSE = -inf; -inf here makes every P of it exactly 0
+        // (exp2(s * c - inf)), and so its dS.
+        neg_lse2 = l == -INFINITY ? -INFINITY : -l * kLog2e;
+        neg_delta_s = -s * kSoftmaxScale;
     }
-    if (lane == 0) ld[w] = out;
+    if (lane == 0) {
+        float* out = reinterpret_cast<float*>(ld) + (w >> 1) * 4 + (w & 1);
+        out[0] = neg_lse2;
+        out[2] = neg_delta_s;
+    }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -134,27 +150,6 @@ __global__ void __launch_bounds__(256) bwd_dq_convert_kernel(const float* __rest
             uint4 w4 = make_uint4(a.x, a.y, b.x, b.y);
             reinterpret_cast<uint4*>(dq + (bh * Sq + grow) * 128)[c] = w4;
         }
-    }
-}
-
-// ------------------------------------------------------------------------------------------
-// D[128 x 128] (+)= A * B, A K-major in smem ([m][k]), B MN-major in smem ([k][n]).
-__device__ __forceinline__ void mma_tile_km(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem,
-                                            bool accumulate) {
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        const uint32_t aoff = static_cast<uint32_t>(k >> 2) * kPanelBytes + static_cast<uint32_t>(k & 3) * 32u;
-        umma_ss(d_tmem, umma_desc_kmajor(a_smem + aoff), umma_desc_mnmajor(b_smem + k * 2048u), kIdescKM,
-                (accumulate || k > 0) ? 1u : 0u);
-    }
-}
-// D[128 x 128] (+)= A^T-stored * B, both MN-major in smem: A stored [k][m], B stored [k][n].
-__device__ __forceinline__ void mma_tile_mm(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem,
-                                            bool accumulate) {
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        umma_ss(d_tmem, umma_desc_mnmajor(a_smem + k * 2048u), umma_desc_mnmajor(b_smem + k * 2048u),
-                kIdescMM, (accumulate || k > 0) ? 1u : 0u);
     }
 }
 
@@ -204,15 +199,17 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             mbar_init(bar(kBQFull + s), 1);
             mbar_init(bar(kBQEmpty + s), 1);
         }
-        mbar_init(bar(kBDoFull), 1);
-        mbar_init(bar(kBDoEmpty), 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(bar(kBDoFull + s), 1);
+            mbar_init(bar(kBDoEmpty + s), 2);   // dV (issuer A) and dP^T (issuer B) both read dO
+        }
         mbar_init(bar(kBSFull), 1);
         mbar_init(bar(kBPReady), 256);
         mbar_init(bar(kBDpFull), 1);
         mbar_init(bar(kBDsReady), 256);
         mbar_init(bar(kBDqFull), 1);
         mbar_init(bar(kBDqDrained), 128);
-        mbar_init(bar(kBDkvDone), 1);
+        mbar_init(bar(kBDkvDone), 2);   // last dV (issuer A) and last dK (issuer B)
         mbar_fence_init();
     }
     if (warp == 12) {
@@ -231,15 +228,15 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint32_t tmem = *tmem_slot;
     const uint32_t tST = tmem + 0, tDV = tmem + 128, tDP = tmem + 256, tDK = tmem + 384;
     const uint32_t sK = base + kBwdSmemK, sV = base + kBwdSmemV, sDS = base + kBwdSmemDS;
-    const uint32_t sDO = base + kBwdSmemDO;
+    auto sDO = [&](int s) { return base + kBwdSmemDO + static_cast<uint32_t>(s) * kTileBytes; };
     auto sQ = [&](int s) { return base + kBwdSmemQ + static_cast<uint32_t>(s) * kTileBytes; };
 
     // Register budget: 512 threads x 128 at launch (the whole register file); the MMA/TMA
     // warpgroup gives most of its share to the three warpgroups that hold tile rows in registers.
-    // The four budgets must not exceed 4 x 128 in total (152 * 3 + 56 = 512), or an increase would
+    // The four budgets must not exceed 4 x 128 in total (144 * 3 + 80 = 512), or an increase would
     // wait for registers that are never released.
     if (warp >= 12) {
-      reg_dec<56>();
+      reg_dec<80>();
       if (warp == 13) {
         // ------------------------------------------------------------------ TMA loader
         if (lane == 0 && n_total > 0) {
@@ -270,20 +267,24 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         bulk_load(base + kBwdSmemLD + st * 1024u,
                                   p.ld + (static_cast<long long>(bq) * p.n_mtiles + qt) * 128, 1024,
                                   bar(kBQFull + st));
-                        if (!mbar_wait(bar(kBDoEmpty), (it & 1u) ^ 1u, abort_flag)) {
+                        if (!mbar_wait(bar(kBDoEmpty + st), ((it >> 1) & 1u) ^ 1u, abort_flag)) {
                             report_timeout(p.status, 2, 13, it, 101);
                             ok = false;
                             break;
                         }
-                        mbar_expect_tx(bar(kBDoFull), kTileBytes);
-                        tma_load_3d(sDO, &tm_do, 0, qt * 128, bq, bar(kBDoFull));
-                        tma_load_3d(sDO + kPanelBytes, &tm_do, 64, qt * 128, bq, bar(kBDoFull));
+                        mbar_expect_tx(bar(kBDoFull + st), kTileBytes);
+                        tma_load_3d(sDO(st), &tm_do, 0, qt * 128, bq, bar(kBDoFull + st));
+                        tma_load_3d(sDO(st) + kPanelBytes, &tm_do, 64, qt * 128, bq, bar(kBDoFull + st));
                     }
                 }
             }
         }
     } else if (warp == 12) {
-        // ------------------------------------------------------------------ MMA issuer
+        // ------------------------------------------------------------------ MMA issuer A: dV and S^T
+        // Two issuing threads share the tensor core.  An issuing thread is blocked while its MMAs
+        // execute and while it polls barriers, so with a single thread every wake-up and commit
+        // is tensor-core idle time; thread A runs the chain  P ready -> dV -> next S^T  and
+        // thread B (warp 14) the chain  dS ready -> dQ -> dK -> (dQ drained) -> next dP^T.
         if (lane == 0 && n_total > 0) {
             bool ok = true;
             auto wait = [&](uint32_t slot, uint32_t parity, int it, uint32_t tag) {
@@ -300,30 +301,46 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 mma_tile_kk(tST, sK, sQ(0), false);
                 umma_commit(bar(kBSFull));
             }
-            wait(kBDoFull, 0, 0, 202);
-            if (ok) {
-                tc_fence_after();
-                mma_tile_kk(tDP, sV, sDO, false);
-                umma_commit(bar(kBDpFull));
-            }
             for (int it = 0; it < n_total && ok; ++it) {
                 const int st = it & 1;
-                const uint32_t ph = it & 1u;
+                if (it + 1 < n_total) wait(kBQFull + (st ^ 1), ((it + 1) >> 1) & 1u, it, 211);
                 if (it < 64) FBA_TRACE_REC(p.status, 1024 + it * 8 + 0);
-                wait(kBPReady, ph, it, 210);
+                wait(kBPReady, it & 1u, it, 210);
                 if (!ok) break;
                 tc_fence_after();
                 if (it < 64) FBA_TRACE_REC(p.status, 1024 + it * 8 + 1);
-                mma_tile_tm(tDV, tST, tST + 64, sDO, it > 0);
-                umma_commit(bar(kBDoEmpty));          // dO(it) is free once dV (and the earlier dP) finished
+                mma_tile_tm(tDV, tST, tST + 64, sDO(st), it > 0);
+                umma_commit(bar(kBDoEmpty + st));     // one of the two releases of dO(it)
                 if (it + 1 < n_total) {
-                    wait(kBQFull + (st ^ 1), ((it + 1) >> 1) & 1u, it, 211);
-                    if (!ok) break;
-                    tc_fence_after();
                     mma_tile_kk(tST, sK, sQ(st ^ 1), false);
                     umma_commit(bar(kBSFull));
                 }
                 if (it < 64) FBA_TRACE_REC(p.status, 1024 + it * 8 + 2);
+            }
+            if (ok) umma_commit(bar(kBDkvDone));
+        }
+      } else if (warp == 14) {
+        // ------------------------------------------------------------------ MMA issuer B: dP^T, dQ, dK
+        if (lane == 0 && n_total > 0) {
+            bool ok = true;
+            auto wait = [&](uint32_t slot, uint32_t parity, int it, uint32_t tag) {
+                if (!ok) return;
+                if (!mbar_wait(bar(slot), parity, abort_flag)) {
+                    report_timeout(p.status, 2, 14, it, tag);
+                    ok = false;
+                }
+            };
+            wait(kBKvFull, 0, 0, 220);
+            wait(kBDoFull + 0, 0, 0, 202);
+            if (ok) {
+                tc_fence_after();
+                mma_tile_kk(tDP, sV, sDO(0), false);
+                umma_commit(bar(kBDpFull));
+                umma_commit(bar(kBDoEmpty + 0));      // the other release of dO(0)
+            }
+            for (int it = 0; it < n_total && ok; ++it) {
+                const int st = it & 1;
+                const uint32_t ph = it & 1u;
                 wait(kBDsReady, ph, it, 212);
                 if (!ok) break;
                 tc_fence_after();
@@ -334,14 +351,14 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 umma_commit(bar(kBQEmpty + st));
                 if (it < 64) FBA_TRACE_REC(p.status, 1024 + it * 8 + 4);
                 if (it + 1 < n_total) {
-                    wait(kBDoFull, (it + 1) & 1u, it, 214);
+                    wait(kBDoFull + (st ^ 1), ((it + 1) >> 1) & 1u, it, 214);
                     wait(kBDqDrained, ph, it, 213);
                     if (!ok) break;
                     tc_fence_after();
                     if (it < 64) FBA_TRACE_REC(p.status, 1024 + it * 8 + 5);
-                    mma_tile_kk(tDP, sV, sDO, false);
-                    if (it < 64) FBA_TRACE_REC(p.status, 1024 + it * 8 + 7);
+                    mma_tile_kk(tDP, sV, sDO(st ^ 1), false);
                     umma_commit(bar(kBDpFull));
+                    umma_commit(bar(kBDoEmpty + (st ^ 1)));
                     if (it < 64) FBA_TRACE_REC(p.status, 1024 + it * 8 + 6);
                 }
             }
@@ -350,7 +367,7 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
     } else if (warp >= 8) {
         // ------------------------------------------------------------------ dQ drain
-        reg_inc<152>();
+        reg_inc<144>();
         const int quad = warp & 3;
         const uint32_t tdq = tDP + (static_cast<uint32_t>(quad * 32) << 16);
         int it = 0;
@@ -390,7 +407,7 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                             red_add_v4(dst + cc * 4096 + (j * 32 + lane) * 4, __uint_as_float(v[32 * cc + 4 * j]),
                                        __uint_as_float(v[32 * cc + 4 * j + 1]), __uint_as_float(v[32 * cc + 4 * j + 2]),
                                        __uint_as_float(v[32 * cc + 4 * j + 3]));
-                            __nanosleep(48);
+                            __nanosleep(FBA_RED_SLEEP_NS);
                         }
                     }
                     if (warp == 8 && lane == 0 && it < 64) FBA_TRACE_REC(p.status, it * 8 + 6);
@@ -399,7 +416,7 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
     } else {
         // ------------------------------------------------------------------ P^T / dS^T compute
-        reg_inc<152>();
+        reg_inc<144>();
         const int h = warp >> 2;           // query-column half of the tile
         const int quad = warp & 3;
         const int row = quad * 32 + lane;  // key row inside the tile == TMEM lane
@@ -433,9 +450,11 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         tmem_wait_ld();
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
-                            const float4 l2 = ld4[j];   // (lse2, delta) of columns 2j and 2j+1
-                            pr[2 * j] = ex2_approx(fmaf(__uint_as_float(s[2 * j]), c, -l2.x));
-                            pr[2 * j + 1] = ex2_approx(fmaf(__uint_as_float(s[2 * j + 1]), c, -l2.z));
+                            const float4 l2 = ld4[j];   // (-lse2, -lse2, -delta*scale, -delta*scale) of columns 2j, 2j+1
+                            const float2 x = fma2(make_float2(__uint_as_float(s[2 * j]), __uint_as_float(s[2 * j + 1])),
+                                                  make_float2(c, c), make_float2(l2.x, l2.y));
+                            pr[2 * j] = ex2_approx(x.x);
+                            pr[2 * j + 1] = ex2_approx(x.y);
                         }
                     }
                     if (w != 0xffffu) {
@@ -476,9 +495,10 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         for (int j = 0; j < 4; ++j) {
                             const int col = 8 * q8 + 2 * j;
                             const float4 l2 = ld4[col >> 1];
-                            const float d0 = pr[col] * (__uint_as_float(dp[col]) - l2.y) * kSoftmaxScale;
-                            const float d1 = pr[col + 1] * (__uint_as_float(dp[col + 1]) - l2.w) * kSoftmaxScale;
-                            wds[j] = pack_bf16x2(d0, d1);
+                            const float2 t = fma2(make_float2(__uint_as_float(dp[col]), __uint_as_float(dp[col + 1])),
+                                                  make_float2(kSoftmaxScale, kSoftmaxScale), make_float2(l2.z, l2.w));
+                            const float2 d = mul2(make_float2(pr[col], pr[col + 1]), t);
+                            wds[j] = pack_bf16x2(d.x, d.y);
                         }
                         *reinterpret_cast<uint4*>(ds_row + (static_cast<uint32_t>(q8 ^ (row & 7)) << 4)) =
                             make_uint4(wds[0], wds[1], wds[2], wds[3]);

@@ -59,24 +59,38 @@ __device__ __forceinline__ void report_timeout(uint32_t* status, uint32_t kernel
 // (contraction over the 128 columns).
 __device__ __forceinline__ void mma_tile_kk(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem,
                                             bool accumulate) {
+    const uint32_t a = desc_lo_kmajor(a_smem), b = desc_lo_kmajor(b_smem);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        const uint32_t off = static_cast<uint32_t>(k >> 2) * kPanelBytes + static_cast<uint32_t>(k & 3) * 32u;
-        umma_ss(d_tmem, umma_desc_kmajor(a_smem + off), umma_desc_kmajor(b_smem + off), kIdescKK,
-                (accumulate || k > 0) ? 1u : 0u);
-    }
+    for (int k = 0; k < 8; ++k)
+        umma_ss(d_tmem, a + kstep_kmajor(k), b + kstep_kmajor(k), kIdescKK, (accumulate || k > 0) ? 1u : 0u);
 }
 // D[128 x 128] (+)= A * B with A[128 x 128] bf16 in TMEM (row = lane, 8 columns per 16 k) and
 // B[k = 128 rows][n = 128 columns] MN-major in shared memory.  `a_tmem_hi` is the TMEM address of
 // k-steps 4..7 (A need not be column-contiguous across its two halves).
 __device__ __forceinline__ void mma_tile_tm(uint32_t d_tmem, uint32_t a_tmem_lo, uint32_t a_tmem_hi,
                                             uint32_t b_smem, bool accumulate) {
+    const uint32_t b = desc_lo_mnmajor(b_smem);
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
         const uint32_t a = (k < 4 ? a_tmem_lo : a_tmem_hi) + static_cast<uint32_t>(k & 3) * 8u;
-        umma_ts(d_tmem, a, umma_desc_mnmajor(b_smem + static_cast<uint32_t>(k) * 2048u), kIdescKM,
-                (accumulate || k > 0) ? 1u : 0u);
+        umma_ts(d_tmem, a, b + kstep_mnmajor(k), kIdescKM, (accumulate || k > 0) ? 1u : 0u);
     }
+}
+// D[128 x 128] (+)= A * B, A K-major in smem ([m][k]), B MN-major in smem ([k][n]).
+__device__ __forceinline__ void mma_tile_km(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem,
+                                            bool accumulate) {
+    const uint32_t a = desc_lo_kmajor(a_smem), b = desc_lo_mnmajor(b_smem);
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+        umma_ss(d_tmem, a + kstep_kmajor(k), b + kstep_mnmajor(k), kIdescKM, (accumulate || k > 0) ? 1u : 0u);
+}
+// D[128 x 128] (+)= A^T-stored * B, both MN-major in smem: A stored [k][m], B stored [k][n].
+__device__ __forceinline__ void mma_tile_mm(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem,
+                                            bool accumulate) {
+    const uint32_t a = desc_lo_mnmajor(a_smem), b = desc_lo_mnmajor(b_smem);
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+        umma_ss(d_tmem, a + kstep_mnmajor(k), b + kstep_mnmajor(k), kIdescMM, (accumulate || k > 0) ? 1u : 0u);
 }
 
 }  // namespace fba

@@ -6,7 +6,7 @@
 //
 //   * a CTA owns two 128-row query tiles (A and B) of one (batch, head) and ping-pongs between
 //     them, so the tensor core works on one tile while the softmax warps work on the other;
-//   * one thread issues every tcgen05.mma.  S = Q K^T goes to TMEM (128 fp32 columns per tile),
+//   * one thread per query tile issues that tile's tcgen05.mma.  S = Q K^T goes to TMEM (128 fp32 columns per tile),
 //     the softmax warps read it with tcgen05.ld (one thread = one row, so row max / row sum need
 //     no shuffles), write P back as bf16 into the same columns, and O += P V consumes P
 //     straight from TMEM; O (128 fp32 columns per tile) never leaves TMEM until the epilogue.
@@ -15,9 +15,8 @@
 //     TMA + mbarrier; the list comes from the compaction kernel, not from scanning the mask;
 //   * rescaling of O is lazy (only when the running row max grew by more than 2^8), done by the
 //     softmax warps between two MMAs of their tile;
-//   * P reaches the tensor core in two halves (keys 0-63, then 64-127) so O += P V starts while the
-//     second half of the exponentials is still being computed, and a fixed fraction of the
-//     exponentials is evaluated by a polynomial on the FMA pipe to unload the special-function unit.
+//   * optionally a fixed fraction of the exponentials is evaluated by a polynomial on the FMA pipe
+//     to unload the special-function unit (FBA_FWD_POLY_PAIRS).
 //
 // If both query tiles map to the same list row they share every K / V stage; otherwise each tile
 // streams its own list ("split" mode) in a fixed interleaving that loader and issuer both follow.
@@ -25,7 +24,7 @@
 
 namespace fba {
 
-constexpr int kFwdThreads = 384;  // warpgroup 0: softmax A, 1: softmax B, 2: {MMA issue, TMA, 2 idle warps}
+constexpr int kFwdThreads = 384;  // warpgroup 0: softmax A, 1: softmax B, 2: {MMA A, TMA, MMA B, idle}
 constexpr int kFwdStages = 5;
 constexpr uint32_t kFwdSmemQ = 0;
 constexpr uint32_t kFwdSmemRing = 2 * kTileBytes;
@@ -52,20 +51,22 @@ enum FwdBar : uint32_t {
     kBarRingFull = 2,                      // kFwdStages
     kBarRingEmpty = 2 + kFwdStages,        // kFwdStages
     kBarSFull = 2 + 2 * kFwdStages,        // 2
-    kBarPLo = 4 + 2 * kFwdStages,          // 2: P columns 0-63 (keys 0-63 of the tile) are in TMEM
-    kBarPHi = 6 + 2 * kFwdStages,          // 2: keys 64-127
+    kBarPReady = 4 + 2 * kFwdStages,       // 2: P of the tile is in TMEM
+    kBarTurn = 6 + 2 * kFwdStages,         // 2: the other tile's issuer has issued its block
     kBarODone = 8 + 2 * kFwdStages,        // 2
     kBarCount = 10 + 2 * kFwdStages
 };
+static_assert(8 * kBarCount + 16 <= 256, "barrier block overflows its 256-byte slot");
+static_assert(kFwdSmemBytes <= 232448, "exceeds the 227 KiB shared memory of an sm_100 CTA");
 
 // One half (4 k-steps = 64 keys) of O += P V.
 __device__ __forceinline__ void mma_pv_half(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_smem, int half,
                                             bool accumulate) {
+    const uint32_t b = desc_lo_mnmajor(v_smem);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         const int kk = half * 4 + k;
-        umma_ts(d_tmem, p_tmem + static_cast<uint32_t>(kk) * 8u,
-                umma_desc_mnmajor(v_smem + static_cast<uint32_t>(kk) * 2048u), kIdescKM,
+        umma_ts(d_tmem, p_tmem + static_cast<uint32_t>(kk) * 8u, b + kstep_mnmajor(kk), kIdescKM,
                 (accumulate || kk > 0) ? 1u : 0u);
     }
 }
@@ -106,12 +107,12 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         mbar_init(bar(kBarQFull + 1), 1);
         for (int s = 0; s < kFwdStages; ++s) {
             mbar_init(bar(kBarRingFull + s), 1);
-            mbar_init(bar(kBarRingEmpty + s), 1);
+            mbar_init(bar(kBarRingEmpty + s), 2);
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(bar(kBarSFull + t), 1);
-            mbar_init(bar(kBarPLo + t), 128);
-            mbar_init(bar(kBarPHi + t), 128);
+            mbar_init(bar(kBarPReady + t), 128);
+            mbar_init(bar(kBarTurn + t), 1);
             mbar_init(bar(kBarODone + t), 1);
         }
         mbar_fence_init();
@@ -184,78 +185,92 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     }
                 }
             }
-        } else if (warp == 8) {
-            // -------------------------------------------------------------- MMA issuer
-            if (lane == 0) {
+        } else if (warp == 8 || warp == 10) {
+            // -------------------------------------------------------------- MMA issuers
+            // One issuing thread per query tile (warp 8: tile A, warp 10: tile B).  A tile's chain
+            // S -> softmax -> P V -> next S is serial, and the issuing thread is blocked while its
+            // MMAs execute and while it polls barriers; with one thread per tile those bubbles are
+            // filled by the other tile's MMAs.
+            const int t = warp == 8 ? 0 : 1;
+            const int nt = t ? n1 : n0;
+            if (lane == 0 && nt > 0) {
                 bool ok = true;
-                uint32_t cons = 0;
-                const int n[2] = {n0, n1};
-                const uint32_t sQ[2] = {sQ0, sQ1};
-                const uint32_t tS[2] = {tmem + 0, tmem + 128};
-                const uint32_t tO[2] = {tmem + 256, tmem + 384};
-                auto acquire = [&](uint32_t tag) -> int {
-                    const int s = cons % kFwdStages;
-                    if (!mbar_wait(bar(kBarRingFull + s), (cons / kFwdStages) & 1u, abort_flag)) {
-                        report_timeout(p.status, 1, 8, cons, tag);
+                const uint32_t sQt = t ? sQ1 : sQ0;
+                const uint32_t tS = tmem + static_cast<uint32_t>(t) * 128u;
+                const uint32_t tO = tmem + 256u + static_cast<uint32_t>(t) * 128u;
+                const int ln1 = shared_mode ? 0 : n1;   // what the loader streams for tile B
+                // Position of an operand in the loader's global order -> ring slot and parity.
+                auto wait_full = [&](uint32_t pos, uint32_t tag) -> int {
+                    const int s = pos % kFwdStages;
+                    if (!mbar_wait(bar(kBarRingFull + s), (pos / kFwdStages) & 1u, abort_flag)) {
+                        report_timeout(p.status, 1, static_cast<uint32_t>(warp), pos, tag);
                         ok = false;
                     }
-                    ++cons;
                     return s;
                 };
-                int slot_k[2] = {0, 0}, slot_v[2] = {0, 0};
-                // Prologue: S(0) of both tiles.
-                for (int t = 0; t < 2 && ok; ++t) {
-                    if (n[t] == 0) continue;
-                    if (!mbar_wait(bar(kBarQFull + t), 0, abort_flag)) {
-                        report_timeout(p.status, 1, 8, 0, 300 + t);
+                // Every ring slot needs two releases per use: one from each tile's issuer when the
+                // tiles share the stream, both from the only consumer otherwise.
+                auto release = [&](int s) {
+                    umma_commit(bar(kBarRingEmpty + s));
+                    if (!shared_mode) umma_commit(bar(kBarRingEmpty + s));
+                };
+                // Loader order: K(A,0) K(B,0), then per step i: V(A,i) K(A,i+1) V(B,i) K(B,i+1).
+                uint32_t g = (n0 > 0 ? 1u : 0u) + (ln1 > 0 ? 1u : 0u);   // loads before step 0
+                const uint32_t pos_k0 = (t == 1 && !shared_mode) ? (n0 > 0 ? 1u : 0u) : 0u;
+                if (!mbar_wait(bar(kBarQFull + t), 0, abort_flag)) {
+                    report_timeout(p.status, 1, static_cast<uint32_t>(warp), 0, 300 + t);
+                    ok = false;
+                }
+                int slot_k = wait_full(pos_k0, 310 + t);
+                if (ok) {
+                    tc_fence_after();
+                    mma_tile_kk(tS, sQt, ring(slot_k), false);
+                    umma_commit(bar(kBarSFull + t));
+                    release(slot_k);
+                }
+                for (int i = 0; i < nt && ok; ++i) {
+                    const uint32_t a_v = (i < n0), a_k = (i + 1 < n0), b_v = (i < ln1), b_k = (i + 1 < ln1);
+                    const bool own_a = t == 0 || shared_mode;
+                    const uint32_t pos_v = own_a ? g : g + a_v + a_k;
+                    const uint32_t pos_k = pos_v + 1;
+                    g += a_v + a_k + b_v + b_k;
+                    const bool more = i + 1 < nt;
+                    // Both operands of this step were requested long ago; check them before the
+                    // wait for P so that nothing but the MMAs follows it.
+                    const int slot_v = wait_full(pos_v, 330 + t);
+                    if (more) slot_k = wait_full(pos_k, 340 + t);
+                    if (!ok) break;
+                    if (i < 64) FBA_TRACE_REC(p.status, 1024 + i * 8 + t * 4 + 0);
+                    if (!mbar_wait_hot(bar(kBarPReady + t), i & 1u, abort_flag)) {
+                        report_timeout(p.status, 1, static_cast<uint32_t>(warp), i, 320 + t);
                         ok = false;
                         break;
                     }
-                    const bool reuse = shared_mode && t == 1;
-                    slot_k[t] = reuse ? slot_k[0] : acquire(310 + t);
-                    if (!ok) break;
-                    tc_fence_after();
-                    mma_tile_kk(tS[t], sQ[t], ring(slot_k[t]), false);
-                    umma_commit(bar(kBarSFull + t));
-                    if (!shared_mode || t == 1) umma_commit(bar(kBarRingEmpty + slot_k[t]));
-                }
-                const int nmax = n[0] > n[1] ? n[0] : n[1];
-                for (int i = 0; i < nmax && ok; ++i) {
-                    for (int t = 0; t < 2 && ok; ++t) {
-                        if (i >= n[t]) continue;
-                        const bool reuse = shared_mode && t == 1;
-                        const bool release = !shared_mode || t == 1;
-                        if (i < 64) FBA_TRACE_REC(p.status, 1024 + i * 8 + t * 4 + 0);
-                        slot_v[t] = reuse ? slot_v[0] : acquire(330 + t);
-                        if (!ok) break;
-                        if (!mbar_wait(bar(kBarPLo + t), i & 1u, abort_flag)) {
-                            report_timeout(p.status, 1, 8, i, 320 + t);
-                            ok = false;
-                            break;
-                        }
-                        tc_fence_after();
-                        if (i < 64) FBA_TRACE_REC(p.status, 1024 + i * 8 + t * 4 + 1);
-                        mma_pv_half(tO[t], tS[t], ring(slot_v[t]), 0, i > 0);
-                        if (!mbar_wait(bar(kBarPHi + t), i & 1u, abort_flag)) {
-                            report_timeout(p.status, 1, 8, i, 325 + t);
-                            ok = false;
-                            break;
-                        }
-                        tc_fence_after();
-                        mma_pv_half(tO[t], tS[t], ring(slot_v[t]), 1, true);
-                        if (release) umma_commit(bar(kBarRingEmpty + slot_v[t]));
-                        if (i + 1 < n[t]) {
-                            slot_k[t] = reuse ? slot_k[0] : acquire(340 + t);
-                            if (!ok) break;
-                            tc_fence_after();
-                            mma_tile_kk(tS[t], sQ[t], ring(slot_k[t]), false);
-                            umma_commit(bar(kBarSFull + t));
-                            if (release) umma_commit(bar(kBarRingEmpty + slot_k[t]));
-                        } else {
-                            umma_commit(bar(kBarODone + t));
-                        }
-                        if (i < 64) FBA_TRACE_REC(p.status, 1024 + i * 8 + t * 4 + 2);
+                    // Blocks are issued in the fixed order A(0) B(0) A(1) B(1) ...: that keeps the
+                    // two tiles half a period apart, so one tile's softmax always overlaps the
+                    // other tile's MMAs instead of both softmaxes competing for the same units.
+                    const bool wait_turn = t == 0 ? (i >= 1 && i - 1 < n1) : (i < n0);
+                    if (wait_turn && !mbar_wait_hot(bar(kBarTurn + t), (t == 0 ? i - 1 : i) & 1u, abort_flag)) {
+                        report_timeout(p.status, 1, static_cast<uint32_t>(warp), i, 350 + t);
+                        ok = false;
+                        break;
                     }
+                    tc_fence_after();
+                    if (i < 64) FBA_TRACE_REC(p.status, 1024 + i * 8 + t * 4 + 1);
+                    mma_pv_half(tO, tS, ring(slot_v), 0, i > 0);
+                    mma_pv_half(tO, tS, ring(slot_v), 1, true);
+                    if (more) {
+                        mma_tile_kk(tS, sQt, ring(slot_k), false);
+                        umma_commit(bar(kBarSFull + t));
+                        mbar_arrive(bar(kBarTurn + (t ^ 1)));
+                        release(slot_v);
+                        release(slot_k);
+                    } else {
+                        umma_commit(bar(kBarODone + t));
+                        mbar_arrive(bar(kBarTurn + (t ^ 1)));
+                        release(slot_v);
+                    }
+                    if (i < 64) FBA_TRACE_REC(p.status, 1024 + i * 8 + t * 4 + 2);
                 }
             }
         }
@@ -350,33 +365,25 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             l2b.y *= alpha;
             const float neg_off = have_off ? -off : 0.f;
             const float2 noff2 = make_float2(neg_off, neg_off);
+            uint32_t pk[64];
 #pragma unroll
-            for (int cc = 0; cc < 4; ++cc) {
-                uint32_t pk[16];
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const float2 x = fma2(make_float2(__uint_as_float(u[32 * cc + 2 * j]), __uint_as_float(u[32 * cc + 2 * j + 1])),
-                                          c2, noff2);
-                    float2 e;
-                    if (j < FBA_FWD_POLY_PAIRS) {
-                        e = ex2_poly2(x);
-                    } else {
-                        e.x = ex2_approx(x.x);
-                        e.y = ex2_approx(x.y);
-                    }
-                    if (j & 1) l2b = add2(l2b, e); else l2a = add2(l2a, e);
-                    pk[j] = pack_bf16x2(e.x, e.y);
+            for (int j = 0; j < 64; ++j) {
+                const float2 x = fma2(make_float2(__uint_as_float(u[2 * j]), __uint_as_float(u[2 * j + 1])), c2, noff2);
+                float2 e;
+                if ((j & 15) < FBA_FWD_POLY_PAIRS) {
+                    e = ex2_poly2(x);
+                } else {
+                    e.x = ex2_approx(x.x);
+                    e.y = ex2_approx(x.y);
                 }
-                tmem_st16(tS + 16u * cc, pk);
-                if (cc == 1) {
-                    tmem_wait_st();
-                    tc_fence_before();
-                    mbar_arrive(bar(kBarPLo + t));
-                }
+                if (j & 1) l2b = add2(l2b, e); else l2a = add2(l2a, e);
+                pk[j] = pack_bf16x2(e.x, e.y);
             }
+            tmem_st32(tS, reinterpret_cast<uint32_t(&)[32]>(pk[0]));
+            tmem_st32(tS + 32u, reinterpret_cast<uint32_t(&)[32]>(pk[32]));
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(bar(kBarPHi + t));
+            mbar_arrive(bar(kBarPReady + t));
             if (tracer && i < 64) FBA_TRACE_REC(p.status, i * 8 + t * 4 + 3);
         }
         const float l = (l2a.x + l2a.y) + (l2b.x + l2b.y);

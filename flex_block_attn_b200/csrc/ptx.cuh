@@ -133,6 +133,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Bounded wait.  Every spin in these kernels goes through here: after `kWaitLimitCycles` SM
 // clocks without the phase completing (or as soon as another role of the CTA raised the abort
 // flag) the wait gives up, raises the CTA-wide abort flag and returns false; the caller then
@@ -149,6 +161,24 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         __nanosleep(FBA_SPIN_SLEEP_NS);
 #endif
         if (((++it) & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kWaitLimitCycles) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
+// Same contract as mbar_wait, but polls with the non-suspending test_wait: lower wake-up latency
+// at the price of issue slots, for the single-thread roles whose wake-up is on the critical path.
+__device__ __forceinline__ bool mbar_wait_hot(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_test_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t it = 0;
+    while (true) {
+        if (mbar_test_wait(bar, parity)) return true;
+        if (((++it) & 1023u) == 0u) {
             if (*abort_flag) return false;
             if (clock64() - t0 > kWaitLimitCycles) {
                 *abort_flag = 1;
@@ -305,37 +335,42 @@ __host__ __device__ constexpr uint32_t umma_idesc(int M, int N, int a_mn_major, 
 //  * MN-major use (the contraction runs down the rows): the 64-element row is the MN extent of
 //    one swizzle atom, LBO = 16384 (next panel = next 64 MN elements), SBO = 1024 (next 8 rows of
 //    K).  One MMA consumes 16 rows; step k by adding 2048 bytes.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes,
-                                              uint32_t sbo_bytes) {
-    return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) |
-           (static_cast<uint64_t>(lbo_bytes >> 4) << 16) |
-           (static_cast<uint64_t>(sbo_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
+// The descriptor is handled as two 32-bit halves so that stepping through k is one 32-bit add on
+// the low half (shared-memory addresses are below 2^18, so (addr >> 4) never carries out of the
+// 14-bit address field): the issuing thread shares its scheduler with busy softmax warps, and
+// every instruction it spends per MMA shows up as tensor-core idle time.
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128B swizzle
+__device__ __forceinline__ uint32_t desc_lo_kmajor(uint32_t smem_addr) { return (smem_addr >> 4) | (1u << 16); }
+__device__ __forceinline__ uint32_t desc_lo_mnmajor(uint32_t smem_addr) {
+    return (smem_addr >> 4) | ((16384u >> 4) << 16);
 }
-__device__ __forceinline__ uint64_t umma_desc_kmajor(uint32_t smem_addr) {
-    return umma_desc(smem_addr, 16, 1024);
+// k-step strides of the low half: K-major 32 bytes inside a panel and 16 KiB between panels;
+// MN-major 2048 bytes (16 rows).
+__device__ __forceinline__ constexpr uint32_t kstep_kmajor(int k) {
+    return static_cast<uint32_t>(k >> 2) * (16384u >> 4) + static_cast<uint32_t>(k & 3) * 2u;
 }
-__device__ __forceinline__ uint64_t umma_desc_mnmajor(uint32_t smem_addr) {
-    return umma_desc(smem_addr, 16384, 1024);
-}
+__device__ __forceinline__ constexpr uint32_t kstep_mnmajor(int k) { return static_cast<uint32_t>(k) * (2048u >> 4); }
 
 // D[tmem] (+)= A[smem] * B[smem].  Issued by ONE thread.
-__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                        uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                        uint32_t accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHi)
         : "memory");
 }
 // D[tmem] (+)= A[tmem] * B[smem].  A holds bf16 pairs, 8 columns per 16-element k step.
-__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
-                                        uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc,
+                                        uint32_t accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        "mov.b64 db, {%2, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHi)
         : "memory");
 }
 // Make `bar` observe completion of every tcgen05.mma this thread issued so far.
