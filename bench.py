@@ -48,9 +48,12 @@ FLOPS_PER_PAIR = FLOPS_PER_PAIR_FWD + FLOPS_PER_PAIR_BWD
 METRIC = "fwd+bwd effective TFLOPS (active blocks), S=69120 sparse 0.6; % B200 bf16 peak"
 
 # DRAM traffic of the backward main kernel per active 384x384 block pair, from the ncu capture
-# summarised in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum divided by the pairs of
-# the captured launch); None until a capture exists.
-BWD_DRAM_BYTES_PER_PAIR = None
+# summarised in profiles/fba_bwd_kernel_s23040_h8.md: (dram__bytes_read.sum + dram__bytes_write.sum)
+# = 431.0 MB for the 11 805 pairs of the captured launch.  The bench workload is too large to capture
+# under the size rule, so `roofline.traffic` scales this figure by the pairs of a full launch; in
+# the captured case the dQ accumulator is L2-resident, at full size it is not, so the true figure is
+# higher than this proportional scaling.
+BWD_DRAM_BYTES_PER_PAIR = 431.0e6 / 11805
 
 
 def parse_args():
@@ -378,6 +381,7 @@ def main():
         "frac_of_burst_peak": achieved / peaks["burst"], "burst_peak": peaks["burst"],
         "ms_per_launch": bwd_ms, "flops_per_launch": bwd_flops,
         "traffic": (BWD_DRAM_BYTES_PER_PAIR * nnz_local) if BWD_DRAM_BYTES_PER_PAIR else None,
+        "traffic_note": "bytes per launch, scaled per active pair from the ncu capture of a smaller case (profiles/)",
         "share_of_step": bwd_ms / ms_local,
     }
     if fwd_ms:
