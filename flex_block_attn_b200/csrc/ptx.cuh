@@ -220,6 +220,13 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, int x, int y,
         "r"(src_smem), "r"(x), "r"(y), "r"(z)
         : "memory");
 }
+// Pull a tile into L2 ahead of the load that will need it.
+__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* m, int x, int y, int z) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(
+                     reinterpret_cast<uint64_t>(m)),
+                 "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
 // Untiled bulk copy global -> shared (both 16-byte aligned, size a multiple of 16).
 __device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes,
                                           uint32_t bar) {
