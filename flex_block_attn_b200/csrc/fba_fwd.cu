@@ -51,10 +51,11 @@ enum FwdBar : uint32_t {
     kBarRingFull = 2,                      // kFwdStages
     kBarRingEmpty = 2 + kFwdStages,        // kFwdStages
     kBarSFull = 2 + 2 * kFwdStages,        // 2
-    kBarPReady = 4 + 2 * kFwdStages,       // 2: P of the tile is in TMEM
-    kBarTurn = 6 + 2 * kFwdStages,         // 2: the other tile's issuer has issued its block
-    kBarODone = 8 + 2 * kFwdStages,        // 2
-    kBarCount = 10 + 2 * kFwdStages
+    kBarPReady = 4 + 2 * kFwdStages,       // 2: P columns of keys 0-63 of the tile are in TMEM
+    kBarPHi = 6 + 2 * kFwdStages,          // 2: keys 64-127
+    kBarTurn = 8 + 2 * kFwdStages,         // 2: the other tile's issuer has issued its block
+    kBarODone = 10 + 2 * kFwdStages,       // 2
+    kBarCount = 12 + 2 * kFwdStages
 };
 static_assert(8 * kBarCount + 16 <= 256, "barrier block overflows its 256-byte slot");
 static_assert(kFwdSmemBytes <= 232448, "exceeds the 227 KiB shared memory of an sm_100 CTA");
@@ -112,6 +113,7 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int t = 0; t < 2; ++t) {
             mbar_init(bar(kBarSFull + t), 1);
             mbar_init(bar(kBarPReady + t), 128);
+            mbar_init(bar(kBarPHi + t), 128);
             mbar_init(bar(kBarTurn + t), 1);
             mbar_init(bar(kBarODone + t), 1);
         }
@@ -241,7 +243,7 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     if (more) slot_k = wait_full(pos_k, 340 + t);
                     if (!ok) break;
                     if (i < 64) FBA_TRACE_REC(p.status, 1024 + i * 8 + t * 4 + 0);
-                    if (!mbar_wait_hot(bar(kBarPReady + t), i & 1u, abort_flag)) {
+                    if (!mbar_wait(bar(kBarPReady + t), i & 1u, abort_flag)) {
                         report_timeout(p.status, 1, static_cast<uint32_t>(warp), i, 320 + t);
                         ok = false;
                         break;
@@ -250,7 +252,7 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     // two tiles half a period apart, so one tile's softmax always overlaps the
                     // other tile's MMAs instead of both softmaxes competing for the same units.
                     const bool wait_turn = t == 0 ? (i >= 1 && i - 1 < n1) : (i < n0);
-                    if (wait_turn && !mbar_wait_hot(bar(kBarTurn + t), (t == 0 ? i - 1 : i) & 1u, abort_flag)) {
+                    if (wait_turn && !mbar_wait(bar(kBarTurn + t), (t == 0 ? i - 1 : i) & 1u, abort_flag)) {
                         report_timeout(p.status, 1, static_cast<uint32_t>(warp), i, 350 + t);
                         ok = false;
                         break;
@@ -258,6 +260,12 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     tc_fence_after();
                     if (i < 64) FBA_TRACE_REC(p.status, 1024 + i * 8 + t * 4 + 1);
                     mma_pv_half(tO, tS, ring(slot_v), 0, i > 0);
+                    if (!mbar_wait(bar(kBarPHi + t), i & 1u, abort_flag)) {
+                        report_timeout(p.status, 1, static_cast<uint32_t>(warp), i, 325 + t);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
                     mma_pv_half(tO, tS, ring(slot_v), 1, true);
                     if (more) {
                         mma_tile_kk(tS, sQt, ring(slot_k), false);
@@ -365,25 +373,31 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             l2b.y *= alpha;
             const float neg_off = have_off ? -off : 0.f;
             const float2 noff2 = make_float2(neg_off, neg_off);
-            uint32_t pk[64];
+            // P goes to TMEM in two halves (keys 0-63, then 64-127) so that O += P V can start
+            // while the second half of the exponentials is still being computed.
 #pragma unroll
-            for (int j = 0; j < 64; ++j) {
-                const float2 x = fma2(make_float2(__uint_as_float(u[2 * j]), __uint_as_float(u[2 * j + 1])), c2, noff2);
-                float2 e;
-                if ((j & 15) < FBA_FWD_POLY_PAIRS) {
-                    e = ex2_poly2(x);
-                } else {
-                    e.x = ex2_approx(x.x);
-                    e.y = ex2_approx(x.y);
+            for (int hh = 0; hh < 2; ++hh) {
+                uint32_t pk[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int jj = 32 * hh + j;
+                    const float2 x = fma2(make_float2(__uint_as_float(u[2 * jj]), __uint_as_float(u[2 * jj + 1])), c2, noff2);
+                    float2 e;
+                    if ((j & 15) < FBA_FWD_POLY_PAIRS) {
+                        e = ex2_poly2(x);
+                    } else {
+                        e.x = ex2_approx(x.x);
+                        e.y = ex2_approx(x.y);
+                    }
+                    if (j & 1) l2b = add2(l2b, e); else l2a = add2(l2a, e);
+                    pk[j] = pack_bf16x2(e.x, e.y);
                 }
-                if (j & 1) l2b = add2(l2b, e); else l2a = add2(l2a, e);
-                pk[j] = pack_bf16x2(e.x, e.y);
+                tmem_st32(tS + 32u * hh, pk);
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(bar((hh ? kBarPHi : kBarPReady) + t));
+                if (hh == 0 && tracer && i < 64) FBA_TRACE_REC(p.status, 3072 + i * 4 + t);
             }
-            tmem_st32(tS, reinterpret_cast<uint32_t(&)[32]>(pk[0]));
-            tmem_st32(tS + 32u, reinterpret_cast<uint32_t(&)[32]>(pk[32]));
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(bar(kBarPReady + t));
             if (tracer && i < 64) FBA_TRACE_REC(p.status, i * 8 + t * 4 + 3);
         }
         const float l = (l2a.x + l2a.y) + (l2b.x + l2b.y);
