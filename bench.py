@@ -168,7 +168,7 @@ def cpu_baseline(S: int, keep: float, target_s: float = 12.0):
     cpu_sample_run(min(S, 3840), keep, 1)  # warm-up of the torch CPU kernels
     nq = 8 if S >= 8 * QB else max(1, S // QB)
     dt, pairs = cpu_sample_run(S, keep, nq)
-    reps = max(1, min(8, int(round(target_s / max(dt, 1e-3)))))
+    reps = max(1, min(24, int(round(target_s / max(dt, 1e-3)))))
     for r in range(1, reps):
         d, p = cpu_sample_run(S, keep, nq, seed=1234 + r)
         dt += d

@@ -72,7 +72,7 @@ static_assert(kBwdSmemBytes <= 232448, "exceeds the 227 KiB shared memory of an 
 
 struct BwdParams {
     ListDev list;          // key-major: rows = key tiles / rows_div, entries = query tiles / sub
-    const float2* ld;      // [B*Hq, nMt*128] (lse * log2e, delta)
+    const float2* ld;      // [B*Hq, nMt, 2, 128]: per query tile 128 x (-lse*log2e), then 128 x (-delta/sqrt(128))
     float* dq_accum;       // [B*Hq, nMt, 4 column chunks, 4 row groups, 8, 32, 4] fp32
     uint32_t* status;
     int n_mtiles, Hq, Hkv;
@@ -89,9 +89,9 @@ __global__ void __launch_bounds__(256) bwd_prep_kernel(const __nv_bfloat16* __re
     const int lane = threadIdx.x & 31;
     const long long bh = w / rows_pad;
     const int r = static_cast<int>(w % rows_pad);
-    // Output layout, per pair of consecutive rows (2j, 2j+1): (-lse2[2j], -lse2[2j+1],
-    // -delta[2j] / sqrt(128), -delta[2j+1] / sqrt(128)), so the main kernel reads one 16-byte word
-    // per column pair and feeds it straight into packed fused multiply-adds.
+    // Output layout, per 128-row query tile: 128 x (-lse2) followed by 128 x (-delta / sqrt(128)),
+    // so the main kernel fetches four columns' worth of either quantity with one 16-byte
+    // shared-memory read and feeds it straight into packed fused multiply-adds.
     float neg_lse2 = -INFINITY, neg_delta_s = 0.f;
     if (r < Sq) {
         const long long row = bh * Sq + r;
@@ -116,9 +116,9 @@ __global__ void __launch_bounds__(256) bwd_prep_kernel(const __nv_bfloat16* __re
         neg_delta_s = -s * kSoftmaxScale;
     }
     if (lane == 0) {
-        float* out = reinterpret_cast<float*>(ld) + (w >> 1) * 4 + (w & 1);
+        float* out = reinterpret_cast<float*>(ld) + (w >> 7) * 256 + (w & 127);
         out[0] = neg_lse2;
-        out[2] = neg_delta_s;
+        out[128] = neg_delta_s;
     }
 }
 
@@ -476,7 +476,8 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 const uint32_t w = p.list.msk ? p.list.msk[lr * p.list.stride + e] : 0xffffu;
                 for (int u = 0; u < sub && ok; ++u, ++it) {
                     const int st = it & 1;
-                    const float4* ld4 = reinterpret_cast<const float4*>(base_ptr + kBwdSmemLD + st * 1024) + 32 * h;
+                    const float4* lse4 = reinterpret_cast<const float4*>(base_ptr + kBwdSmemLD + st * 1024) + 16 * h;
+                    const float4* del4 = lse4 + 32;
                     if (!mbar_wait(bar(kBSFull), it & 1u, abort_flag) ||
                         !mbar_wait(bar(kBQFull + st), (it >> 1) & 1u, abort_flag)) {
                         if (lane == 0) report_timeout(p.status, 2, static_cast<uint32_t>(warp), it, 400);
@@ -493,12 +494,16 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         tmem_ld32(tST + lane_base + 64u * h + 32u, reinterpret_cast<uint32_t(&)[32]>(s[32]));
                         tmem_wait_ld();
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const float4 l2 = ld4[j];   // (-lse2, -lse2, -delta*scale, -delta*scale) of columns 2j, 2j+1
-                            const float2 x = fma2(make_float2(__uint_as_float(s[2 * j]), __uint_as_float(s[2 * j + 1])),
-                                                  make_float2(c, c), make_float2(l2.x, l2.y));
-                            pr[2 * j] = ex2_approx(x.x);
-                            pr[2 * j + 1] = ex2_approx(x.y);
+                        for (int j = 0; j < 16; ++j) {
+                            const float4 l4 = lse4[j];   // -lse2 of columns 4j .. 4j+3
+                            const float2 x0 = fma2(make_float2(__uint_as_float(s[4 * j]), __uint_as_float(s[4 * j + 1])),
+                                                   make_float2(c, c), make_float2(l4.x, l4.y));
+                            const float2 x1 = fma2(make_float2(__uint_as_float(s[4 * j + 2]), __uint_as_float(s[4 * j + 3])),
+                                                   make_float2(c, c), make_float2(l4.z, l4.w));
+                            pr[4 * j] = ex2_approx(x0.x);
+                            pr[4 * j + 1] = ex2_approx(x0.y);
+                            pr[4 * j + 2] = ex2_approx(x1.x);
+                            pr[4 * j + 3] = ex2_approx(x1.y);
                         }
                     }
                     if (w != 0xffffu) {
@@ -536,13 +541,17 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     for (int q8 = 0; q8 < 8; ++q8) {
                         uint32_t wds[4];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int col = 8 * q8 + 2 * j;
-                            const float4 l2 = ld4[col >> 1];
-                            const float2 t = fma2(make_float2(__uint_as_float(dp[col]), __uint_as_float(dp[col + 1])),
-                                                  make_float2(kSoftmaxScale, kSoftmaxScale), make_float2(l2.z, l2.w));
-                            const float2 d = mul2(make_float2(pr[col], pr[col + 1]), t);
-                            wds[j] = pack_bf16x2(d.x, d.y);
+                        for (int j = 0; j < 2; ++j) {
+                            const int col = 8 * q8 + 4 * j;
+                            const float4 d4 = del4[col >> 2];   // -delta/sqrt(128) of columns col .. col+3
+                            const float2 t0 = fma2(make_float2(__uint_as_float(dp[col]), __uint_as_float(dp[col + 1])),
+                                                   make_float2(kSoftmaxScale, kSoftmaxScale), make_float2(d4.x, d4.y));
+                            const float2 t1 = fma2(make_float2(__uint_as_float(dp[col + 2]), __uint_as_float(dp[col + 3])),
+                                                   make_float2(kSoftmaxScale, kSoftmaxScale), make_float2(d4.z, d4.w));
+                            const float2 e0 = mul2(make_float2(pr[col], pr[col + 1]), t0);
+                            const float2 e1 = mul2(make_float2(pr[col + 2], pr[col + 3]), t1);
+                            wds[2 * j] = pack_bf16x2(e0.x, e0.y);
+                            wds[2 * j + 1] = pack_bf16x2(e1.x, e1.y);
                         }
                         *reinterpret_cast<uint4*>(ds_row + (static_cast<uint32_t>(q8 ^ (row & 7)) << 4)) =
                             make_uint4(wds[0], wds[1], wds[2], wds[3]);

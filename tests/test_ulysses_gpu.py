@@ -1,0 +1,81 @@
+"""GPU, >= 2 devices: the Ulysses path (NCCL sequence<->head exchange around the kernels) gives each
+rank the same output and gradients as one GPU computing the whole problem.  Skipped on one GPU."""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, ret):
+    import torch.distributed as dist
+
+    sys.path.insert(0, str(ROOT))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import flex_block_attn_b200 as fba
+        from flex_block_attn_b200 import dist as fd
+        from flex_block_attn_b200 import masks
+        from tests.util import assert_close
+
+        B, H, S, qb, kb = 2, 4, 3072, 128, 384
+        g = torch.Generator().manual_seed(5)
+        full = [torch.randn((B, H, S, 128), generator=g).to(torch.bfloat16).to(dev) for _ in range(4)]
+        Sl = S // world
+        sl = slice(rank * Sl, (rank + 1) * Sl)
+        ql, kl, vl = (t[:, :, sl].contiguous().requires_grad_() for t in full[:3])
+        dol = full[3][:, :, sl].contiguous()
+        grid = (1, 2, 4)  # 8 tiles of 384 tokens
+
+        def mask_fn(qh, kh):
+            return masks.ssta_mask(qh, kh, grid, qb, kb, topk=2)
+
+        o = fd.ulysses_flex_block_attn(ql, kl, vl, qb, kb, mask_fn)
+        o.backward(dol)
+        torch.cuda.synchronize()
+        fba.check_status(dev)
+        # single-GPU computation of the whole problem on this rank's device
+        qf, kf, vf = (t.clone().requires_grad_() for t in full[:3])
+        of = fba.flex_block_attn_func(qf, kf, vf, qb, kb, mask_fn(qf, kf))
+        of.backward(full[3])
+        torch.cuda.synchronize()
+        assert torch.equal(o, of[:, :, sl]), "forward differs from the single-GPU result"
+        assert torch.equal(kl.grad, kf.grad[:, :, sl]) and torch.equal(vl.grad, vf.grad[:, :, sl])
+        assert_close(ql.grad.float(), qf.grad[:, :, sl].float(), "dQ", max_abs=1e-2)
+        ret[rank] = "ok"
+    except Exception as e:  # pragma: no cover - surfaced through ret
+        ret[rank] = f"{type(e).__name__}: {e}"
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_ulysses_two_gpus_match_single_gpu():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    import torch.multiprocessing as mp
+
+    world = 2
+    port = _free_port()
+    with mp.Manager() as m:
+        ret = m.dict()
+        mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
+        assert dict(ret) == {0: "ok", 1: "ok"}
