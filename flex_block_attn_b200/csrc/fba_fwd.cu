@@ -296,7 +296,6 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const uint32_t sQt = t ? sQ1 : sQ0;
         const bool tile_valid = mt < p.n_mtiles;
         const float c = kSoftmaxScale * kLog2e;
-        const float2 c2 = make_float2(c, c);
         const int g = row >> 4;
         const bool tracer = (warp & 3) == 0 && lane == 0;
 
@@ -372,7 +371,6 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             l2b.x *= alpha;
             l2b.y *= alpha;
             const float neg_off = have_off ? -off : 0.f;
-            const float2 noff2 = make_float2(neg_off, neg_off);
             // P goes to TMEM in two halves (keys 0-63, then 64-127) so that O += P V can start
             // while the second half of the exponentials is still being computed.
 #pragma unroll
@@ -381,7 +379,10 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const int jj = 32 * hh + j;
-                    const float2 x = fma2(make_float2(__uint_as_float(u[2 * jj]), __uint_as_float(u[2 * jj + 1])), c2, noff2);
+                    // (plain scalar fused multiply-adds: the packed f32x2 forms measured ~3 % slower here)
+                    float2 x;
+                    x.x = fmaf(__uint_as_float(u[2 * jj]), c, neg_off);
+                    x.y = fmaf(__uint_as_float(u[2 * jj + 1]), c, neg_off);
                     float2 e;
                     if ((j & 15) < FBA_FWD_POLY_PAIRS) {
                         e = ex2_poly2(x);
@@ -389,7 +390,13 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         e.x = ex2_approx(x.x);
                         e.y = ex2_approx(x.y);
                     }
-                    if (j & 1) l2b = add2(l2b, e); else l2a = add2(l2a, e);
+                    if (j & 1) {
+                        l2b.x += e.x;
+                        l2b.y += e.y;
+                    } else {
+                        l2a.x += e.x;
+                        l2a.y += e.y;
+                    }
                     pk[j] = pack_bf16x2(e.x, e.y);
                 }
                 tmem_st32(tS + 32u * hh, pk);
