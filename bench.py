@@ -428,9 +428,9 @@ def main():
     }
     if not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(S, keep)
-    print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    print(json.dumps(line), flush=True)   # last line of stdout
 
 
 if __name__ == "__main__":
