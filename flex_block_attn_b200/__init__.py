@@ -11,6 +11,8 @@ from .interface import (  # noqa: F401
     check_status,
     flex_block_attn_func,
     forward_with_lists,
+    ssta_lists,
+    sta_lists,
 )
 
 __all__ = [
@@ -24,4 +26,6 @@ __all__ = [
     "backward_with_lists",
     "check_status",
     "SparseLists",
+    "sta_lists",
+    "ssta_lists",
 ]

@@ -21,6 +21,9 @@ EXPORTED_SYMBOLS = (
     "fba_set_timing_events",
     "fba_build_index",
     "fba_build_tile_lists",
+    "fba_sta_index",
+    "fba_ssta_scratch_floats",
+    "fba_ssta_index",
     "fba_fwd",
     "fba_bwd_scratch_bytes",
     "fba_bwd",
@@ -72,6 +75,12 @@ def lib() -> ctypes.CDLL:
     L.fba_build_index.argtypes = [vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp]
     L.fba_build_tile_lists.restype = i32
     L.fba_build_tile_lists.argtypes = [vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp]
+    L.fba_sta_index.restype = i32
+    L.fba_sta_index.argtypes = [i32] * 6 + [vp, vp, vp]
+    L.fba_ssta_scratch_floats.restype = i32
+    L.fba_ssta_scratch_floats.argtypes = [i32] * 5 + [ctypes.POINTER(ctypes.c_uint64)]
+    L.fba_ssta_index.restype = i32
+    L.fba_ssta_index.argtypes = [vp, vp] + [i32] * 14 + [vp] * 7
     L.fba_fwd.restype = i32
     L.fba_fwd.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, ctypes.POINTER(FbaList), vp, vp]
     L.fba_bwd_scratch_bytes.restype = i32

@@ -194,6 +194,65 @@ def build_lists(block_mask: torch.Tensor, q_block: int, kv_block: int, Sq: int, 
                        fwd_idx, fwd_cnt, fwd_msk, bwd_idx, bwd_cnt, bwd_msk)
 
 
+def sta_lists(tile_grid, window=(1, 1, 1), tile_tokens: int = 384, device="cuda") -> SparseLists:
+    """Lists of the 3-D sliding-tile mask, built on the device without a bool mask.
+
+    One attention block = one tile of ``tile_tokens`` tokens (a multiple of 128), tokens in
+    tile-major order (``masks.tile_major_permutation``).  Same lists as
+    ``build_lists(masks.sta_mask(tile_grid, window), tile_tokens, tile_tokens, ...)``.
+    """
+    if tile_tokens % TILE != 0:
+        raise ValueError("tile_tokens must be a multiple of 128")
+    Gt, Gh, Gw = tile_grid
+    n = Gt * Gh * Gw
+    dev = torch.device(device)
+    idx = torch.empty((n, n), dtype=torch.int32, device=dev)
+    cnt = torch.empty((n,), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _cabi.lib().fba_sta_index(Gt, Gh, Gw, window[0], window[1], window[2], idx.data_ptr(), cnt.data_ptr(),
+                                       _stream_ptr(dev))
+    _cabi.check(rc, "fba_sta_index")
+    S = n * tile_tokens
+    return SparseLists(True, 2, 1, 1, n, n, tile_tokens, tile_tokens, S, S, idx, cnt, None, idx, cnt, None)
+
+
+def ssta_lists(q, k, tile_grid, q_block: int, kv_block: int, topk: int = 8, window=(1, 1, 1),
+               need_bwd: bool = True):
+    """Hybrid SSTA mask (STA window united with the MoBA top-k of pooled q.k) built by CUDA kernels.
+
+    Returns ``(lists, mask)``: the ``SparseLists`` the attention kernels walk and the bool mask
+    [B, Hq, Sq/q_block, Skv/kv_block] (same definition as ``masks.ssta_mask``).  Both block sizes
+    must be multiples of 128 and q_block must divide kv_block (one key block = one tile).
+    """
+    _check_qkv(q, k, k)
+    if q_block % TILE != 0 or kv_block % TILE != 0:
+        raise ValueError("ssta_lists needs block sizes that are multiples of 128")
+    B, Hq, Sq, _ = q.shape
+    Hkv, Skv = k.shape[1], k.shape[2]
+    nQ, nK = Sq // q_block, Skv // kv_block
+    dev = q.device
+    n = ctypes.c_uint64(0)
+    _cabi.check(_cabi.lib().fba_ssta_scratch_floats(B, Hq, Hkv, nQ, nK, ctypes.byref(n)), "fba_ssta_scratch_floats")
+    scratch = torch.empty((n.value,), dtype=torch.float32, device=dev)
+    mask = torch.empty((B, Hq, nQ, nK), dtype=torch.bool, device=dev)
+    q2k_idx = torch.empty((B * Hq * nQ, nK), dtype=torch.int32, device=dev)
+    q2k_cnt = torch.empty((B * Hq * nQ,), dtype=torch.int32, device=dev)
+    k2q_idx = k2q_cnt = None
+    if need_bwd:
+        k2q_idx = torch.empty((B * Hq * nK, nQ), dtype=torch.int32, device=dev)
+        k2q_cnt = torch.empty((B * Hq * nK,), dtype=torch.int32, device=dev)
+    Gt, Gh, Gw = tile_grid
+    with torch.cuda.device(dev):
+        rc = _cabi.lib().fba_ssta_index(q.data_ptr(), k.data_ptr(), B, Hq, Hkv, Sq, Skv, q_block, kv_block,
+                                        Gt, Gh, Gw, window[0], window[1], window[2], topk, scratch.data_ptr(),
+                                        mask.data_ptr(), q2k_idx.data_ptr(), q2k_cnt.data_ptr(), _ptr(k2q_idx),
+                                        _ptr(k2q_cnt), _stream_ptr(dev))
+    _cabi.check(rc, "fba_ssta_index")
+    lists = SparseLists(True, 4, B, Hq, nQ, nK, q_block, kv_block, Sq, Skv, q2k_idx, q2k_cnt, None, k2q_idx,
+                        k2q_cnt, None)
+    return lists, mask
+
+
 def _check_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
     for name, t in (("q", q), ("k", k), ("v", v)):
         if not t.is_cuda:
@@ -310,7 +369,13 @@ class FlexBlockAttnFunc(torch.autograd.Function):
             f"q_seq_len ({q_seq_len}) must be divisible by q_block_size ({q_block_size})"
         assert kv_seq_len % kv_block_size == 0, \
             f"kv_seq_len ({kv_seq_len}) must be divisible by kv_block_size ({kv_block_size})"
-        if block_mask.dim() == 2:
+        prebuilt = block_mask if isinstance(block_mask, SparseLists) else None
+        if prebuilt is not None:
+            # lists built ahead of time (sta_lists / ssta_lists / build_lists) instead of a bool mask
+            assert (prebuilt.q_block, prebuilt.kv_block) == (q_block_size, kv_block_size), \
+                "the lists were built for other block sizes"
+            q_block_num, kv_block_num = prebuilt.nQ, prebuilt.nK
+        elif block_mask.dim() == 2:
             q_block_num, kv_block_num = block_mask.shape
         else:
             _, _, q_block_num, kv_block_num = block_mask.shape
@@ -322,7 +387,11 @@ class FlexBlockAttnFunc(torch.autograd.Function):
             f"kv_block_size ({kv_block_size}) * kv_block_num ({kv_block_num}) must equal kv_seq_len ({kv_seq_len}"
 
         is_grad = is_grad_enabled and any(x.requires_grad for x in [q, k, v])
-        lists = build_lists(block_mask, q_block_size, kv_block_size, q_seq_len, kv_seq_len, need_bwd=is_grad)
+        if prebuilt is not None:
+            lists = prebuilt
+            assert not is_grad or lists.bwd_idx is not None, "these lists were built without the key-major direction"
+        else:
+            lists = build_lists(block_mask, q_block_size, kv_block_size, q_seq_len, kv_seq_len, need_bwd=is_grad)
         o, lse = forward_with_lists(q, k, v, lists)
         if is_grad:
             ctx.save_for_backward(q, k, v, o, lse)
@@ -345,7 +414,9 @@ def flex_block_attn_func(q, k, v, q_block_size, kv_block_size, block_mask):
         q_block_size: query block size (multiple of 16)
         kv_block_size: key/value block size (multiple of 64; one block size divides the other)
         block_mask: bool [q_seq_len/q_block_size, kv_seq_len/kv_block_size] or
-            [batch, heads, ...same...]; True = the query block attends to the key block
+            [batch, heads, ...same...]; True = the query block attends to the key block.
+            (Extension: a ``SparseLists`` from ``build_lists`` / ``sta_lists`` / ``ssta_lists`` is
+            accepted in its place and skips the compaction.)
 
     Returns:
         [batch, heads, q_seq_len, 128] bf16; differentiable w.r.t. q, k and v.

@@ -104,6 +104,29 @@ int fba_build_tile_lists(const uint8_t* mask, int mask_dim, int B, int H, int nQ
                          uint16_t* bwd_msk, void* stream);
 
 /*
+ * Mask builders that emit lists directly (no counterpart in the reference: it advertises sliding-
+ * tile, MoBA and hybrid SSTA masks, README.md:54-55, but its __init__.py:7-12 leaves them out).
+ *
+ * fba_sta_index: 3-D sliding-tile window over a Gt x Gh x Gw grid of tiles (tile id =
+ * (t*Gh + h)*Gw + w; tile i attends tile j iff |dt|<=wt, |dh|<=wh, |dw|<=ww).  Writes the shared
+ * (2-D) list idx int32 [n, n], cnt int32 [n], n = Gt*Gh*Gw; the relation is symmetric, so the same
+ * list is both the query-major and the key-major one.  Equal to fba_build_index on the bool mask.
+ *
+ * fba_ssta_index: per (batch, head) the STA window of the tile containing each query block,
+ * united with the `topk` key blocks of largest (mean of the query block) . (mean of the key block).
+ * One key block = one tile (Gt*Gh*Gw == Skv/kv_block), q_block divides kv_block.  Writes the bool
+ * mask uint8 [B, Hq, nQ, nK], the query-major list (q2k_idx int32 [B*Hq*nQ, nK], q2k_cnt) and,
+ * if given, the key-major list.  `scratch` holds fba_ssta_scratch_floats() floats.
+ */
+int fba_sta_index(int Gt, int Gh, int Gw, int wt, int wh, int ww, int32_t* idx, int32_t* cnt,
+                  void* stream);
+int fba_ssta_scratch_floats(int B, int Hq, int Hkv, int nQ, int nK, uint64_t* n_floats);
+int fba_ssta_index(const void* q, const void* k, int B, int Hq, int Hkv, int Sq, int Skv, int q_block,
+                   int kv_block, int Gt, int Gh, int Gw, int wt, int wh, int ww, int topk,
+                   float* scratch, uint8_t* mask, int32_t* q2k_idx, int32_t* q2k_cnt,
+                   int32_t* k2q_idx, int32_t* k2q_cnt, void* stream);
+
+/*
  * Forward (replaces attention_forward, reference .cu:810-1007, and fwd_attend_ker, .cu:52-318).
  * `q2k` is the query-major list.  `status` points at 8 zero-initialised uint32 words in device
  * memory; word 0 becomes non-zero if a bounded wait inside the kernel gave up (then the outputs

@@ -1,0 +1,72 @@
+"""GPU: the list-emitting mask builders (fba_sta_index, fba_ssta_index) against the torch builders
+in flex_block_attn_b200/masks.py and the nonzero()-based list oracle."""
+import pytest
+import torch
+
+from oracle import dense_oracle as orc
+from tests.util import rand_qkv
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("grid,window", [((3, 6, 10), (1, 1, 1)), ((1, 1, 5), (0, 0, 2)), ((2, 3, 4), (1, 0, 1)),
+                                         ((4, 4, 4), (3, 3, 3))])
+def test_sta_lists_equal_compacted_mask(grid, window):
+    import flex_block_attn_b200 as fba
+    from flex_block_attn_b200 import masks
+
+    lists = fba.sta_lists(grid, window, tile_tokens=384)
+    mask = masks.sta_mask(grid, window, device="cpu")
+    q2k_idx, q2k_cnt, k2q_idx, k2q_cnt = orc.block_index_oracle(mask)
+    assert torch.equal(lists.fwd_idx.cpu(), q2k_idx) and torch.equal(lists.fwd_cnt.cpu(), q2k_cnt)
+    assert torch.equal(lists.bwd_idx.cpu(), k2q_idx) and torch.equal(lists.bwd_cnt.cpu(), k2q_cnt)
+
+
+def test_sta_lists_drive_the_operator():
+    import flex_block_attn_b200 as fba
+    from flex_block_attn_b200 import masks
+
+    grid = (2, 2, 3)
+    S = 12 * 384
+    q, k, v, do = rand_qkv(1, 2, 2, S, S, seed=90, device="cuda")
+    outs = []
+    for bm in (masks.sta_mask(grid), fba.sta_lists(grid)):
+        qq, kk, vv = (t.clone().requires_grad_() for t in (q, k, v))
+        o = fba.flex_block_attn_func(qq, kk, vv, 384, 384, bm)
+        o.backward(do)
+        outs.append((o.detach(), qq.grad, kk.grad, vv.grad))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][2], outs[1][2]) and torch.equal(outs[0][3], outs[1][3])
+    assert (outs[0][1].float() - outs[1][1].float()).abs().max().item() <= 1e-2
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,grid,qb,kb,topk", [(1, 2, 2, (1, 2, 4), 128, 384, 2), (2, 4, 2, (3, 2, 2), 128, 384, 3),
+                                                     (1, 2, 2, (3, 6, 10), 128, 384, 8), (1, 1, 1, (1, 1, 6), 384, 384, 6)])
+def test_ssta_lists_match_torch_builder(B, Hq, Hkv, grid, qb, kb, topk):
+    import flex_block_attn_b200 as fba
+    from flex_block_attn_b200 import masks
+
+    n_tiles = grid[0] * grid[1] * grid[2]
+    S = n_tiles * kb
+    q, k, _, _ = rand_qkv(B, Hq, Hkv, S, S, seed=91 + topk, device="cuda")
+    lists, mask = fba.ssta_lists(q, k, grid, qb, kb, topk=topk)
+    want = masks.ssta_mask(q, k, grid, qb, kb, topk=topk)
+    assert mask.shape == want.shape and mask.dtype == torch.bool
+    # the lists are exactly the compaction of the mask the kernel produced
+    q2k_idx, q2k_cnt, k2q_idx, k2q_cnt = orc.block_index_oracle(mask.cpu())
+    assert torch.equal(lists.fwd_idx.cpu(), q2k_idx) and torch.equal(lists.fwd_cnt.cpu(), q2k_cnt)
+    assert torch.equal(lists.bwd_idx.cpu(), k2q_idx) and torch.equal(lists.bwd_cnt.cpu(), k2q_cnt)
+    # and the mask is the torch builder's; rows may differ only where pooled scores tie to within
+    # fp32 summation-order noise
+    diff_rows = (mask != want).any(-1)
+    if diff_rows.any():
+        qp = q.float().reshape(B, Hq, S // qb, qb, 128).mean(3)
+        kp = k.float().reshape(B, Hkv, S // kb, kb, 128).mean(3).repeat_interleave(Hq // Hkv, dim=1)
+        score = torch.matmul(qp, kp.transpose(-1, -2))
+        for b, h, r in diff_rows.nonzero().tolist():
+            a, w = mask[b, h, r], want[b, h, r]
+            only_a, only_w = (a & ~w).nonzero().flatten(), (w & ~a).nonzero().flatten()
+            assert len(only_a) == len(only_w)
+            sa, sw = score[b, h, r, only_a].sort().values, score[b, h, r, only_w].sort().values
+            assert torch.allclose(sa, sw, rtol=1e-4, atol=1e-5), "selection differs beyond a numerical tie"
+    assert diff_rows.float().mean().item() < 0.01
+    assert bool((mask.sum(-1) >= min(topk, n_tiles)).all())
