@@ -48,7 +48,7 @@ FLOPS_PER_PAIR = FLOPS_PER_PAIR_FWD + FLOPS_PER_PAIR_BWD
 METRIC = "fwd+bwd effective TFLOPS (active blocks), S=69120 sparse 0.6; % B200 bf16 peak"
 
 # DRAM traffic of the backward main kernel per active 384x384 block pair, from the ncu capture
-# summarised in profiles/fba_bwd_kernel_s23040_h8.md: (dram__bytes_read.sum + dram__bytes_write.sum)
+# summarised under profiles/ (backward kernel, S=23040 H=8 case): (dram__bytes_read.sum + dram__bytes_write.sum)
 # = 431.0 MB for the 11 805 pairs of the captured launch.  The bench workload is too large to capture
 # under the size rule, so `roofline.traffic` scales this figure by the pairs of a full launch; in
 # the captured case the dQ accumulator is L2-resident, at full size it is not, so the true figure is

@@ -1,4 +1,4 @@
-"""GPU: the BASELINE workloads at (or near) their full sizes.  Full-size parity against the fp32 slab
+"""GPU: the benchmark workloads (full, random-sparse, STA, SSTA) at (or near) their full sizes.  Full-size parity against the fp32 slab
 oracle run on the same device for a subset of heads, plus size-independent properties
 (constant-V rows, linearity in V and dO, run-to-run determinism) on the full head count."""
 import pytest

@@ -29,7 +29,7 @@ def test_slab_matches_reference_golden(name):
 
 
 def test_config1_explicit_slab_sdpa_agree():
-    """BASELINE config 1: B=1, H=2, S=1536, D=128, 384-blocks, Bernoulli(0.5)|diag mask, fp32."""
+    """Benchmark configuration 1 (the CPU-runnable case): B=1, H=2, S=1536, D=128, 384-blocks, Bernoulli(0.5)|diag mask, fp32."""
     q, k, v, do = rand_qkv(1, 2, 2, 1536, 1536, seed=0, dtype=torch.float32)
     mask = bernoulli_mask((4, 4), 0.5, seed=0)
     qr, kr, vr = (t.clone().requires_grad_() for t in (q, k, v))
