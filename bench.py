@@ -375,7 +375,7 @@ def main():
 
         run_e2e(0, max(2, min(args.warmup, 3)))
         barrier()
-        n_e2e = max(2, min(args.steps, 5))
+        n_e2e = max(2, min(args.steps, 10))
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record()
         ms_seen = run_e2e(100, n_e2e)
