@@ -24,6 +24,7 @@ EXPORTED_SYMBOLS = (
     "fba_sta_index",
     "fba_ssta_scratch_floats",
     "fba_ssta_index",
+    "fba_tile_major",
     "fba_fwd",
     "fba_bwd_scratch_bytes",
     "fba_bwd",
@@ -81,6 +82,8 @@ def lib() -> ctypes.CDLL:
     L.fba_ssta_scratch_floats.argtypes = [i32] * 5 + [ctypes.POINTER(ctypes.c_uint64)]
     L.fba_ssta_index.restype = i32
     L.fba_ssta_index.argtypes = [vp, vp] + [i32] * 14 + [vp] * 7
+    L.fba_tile_major.restype = i32
+    L.fba_tile_major.argtypes = [vp, vp] + [i32] * 9 + [vp]
     L.fba_fwd.restype = i32
     L.fba_fwd.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, ctypes.POINTER(FbaList), vp, vp]
     L.fba_bwd_scratch_bytes.restype = i32

@@ -86,3 +86,39 @@ def ssta_mask(q: torch.Tensor, k: torch.Tensor, tile_grid: Sequence[int], q_bloc
     win_q = win.repeat_interleave(kv_block // q_block, dim=0)              # [nQ, n_tiles]
     assert win_q.shape[0] == q.shape[2] // q_block
     return moba_topk_mask(q, k, q_block, kv_block, topk) | win_q[None, None]
+
+
+def to_tile_major(x: torch.Tensor, grid: Sequence[int], tile: Sequence[int]) -> torch.Tensor:
+    """[B, S, H, 128] bf16, raster (t, h, w) token order -> [B, H, S, 128], tile-major token order.
+
+    One CUDA pass (transpose + token permutation); equal to
+    ``x.transpose(1, 2)[:, :, tile_major_permutation(grid, tile)]``.
+    """
+    return _tile_major(x, grid, tile, True)
+
+
+def from_tile_major(x: torch.Tensor, grid: Sequence[int], tile: Sequence[int]) -> torch.Tensor:
+    """Inverse of ``to_tile_major``: [B, H, S, 128] tile-major -> [B, S, H, 128] raster order."""
+    return _tile_major(x, grid, tile, False)
+
+
+def _tile_major(x, grid, tile, forward: bool):
+    from . import _cabi
+
+    if not x.is_cuda or x.dtype != torch.bfloat16 or x.dim() != 4 or x.shape[-1] != 128 or not x.is_contiguous():
+        raise ValueError("expected a contiguous CUDA bf16 tensor with a last dimension of 128")
+    T, H, W = grid
+    S = T * H * W
+    if forward:
+        B, S_in, Hn, _ = x.shape
+        out = torch.empty((B, Hn, S, 128), dtype=x.dtype, device=x.device)
+    else:
+        B, Hn, S_in, _ = x.shape
+        out = torch.empty((B, S, Hn, 128), dtype=x.dtype, device=x.device)
+    if S_in != S:
+        raise ValueError(f"sequence length {S_in} does not match the {T}x{H}x{W} grid")
+    with torch.cuda.device(x.device):
+        rc = _cabi.lib().fba_tile_major(x.data_ptr(), out.data_ptr(), B, Hn, T, H, W, tile[0], tile[1], tile[2],
+                                        1 if forward else 0, torch.cuda.current_stream(x.device).cuda_stream)
+    _cabi.check(rc, "fba_tile_major")
+    return out

@@ -127,6 +127,17 @@ int fba_ssta_index(const void* q, const void* k, int B, int Hq, int Hkv, int Sq,
                    int32_t* k2q_idx, int32_t* k2q_cnt, void* stream);
 
 /*
+ * Layout change around the operator, one pass: bf16 [B, S, Hn, 128] with tokens in raster (t, h, w)
+ * order over a T x H x W grid  <->  bf16 [B, Hn, S, 128] with tokens in tile-major order (tiles of
+ * tt x th x tw tokens, tiles in raster order).  Replaces the transpose the reference's callers do
+ * before the call (benchmark/dynamic/random/scripts/random_fwd.py:58-60) plus the token reorder
+ * sliding-tile masks assume.  to_tile_major != 0: src is [B,S,Hn,128], dst [B,Hn,S,128]; else the
+ * inverse.  src and dst must not overlap.
+ */
+int fba_tile_major(const void* src, void* dst, int B, int Hn, int T, int H, int W, int tt, int th, int tw,
+                   int to_tile_major, void* stream);
+
+/*
  * Forward (replaces attention_forward, reference .cu:810-1007, and fwd_attend_ker, .cu:52-318).
  * `q2k` is the query-major list.  `status` points at 8 zero-initialised uint32 words in device
  * memory; word 0 becomes non-zero if a bounded wait inside the kernel gave up (then the outputs

@@ -70,3 +70,19 @@ def test_ssta_lists_match_torch_builder(B, Hq, Hkv, grid, qb, kb, topk):
             assert torch.allclose(sa, sw, rtol=1e-4, atol=1e-5), "selection differs beyond a numerical tie"
     assert diff_rows.float().mean().item() < 0.01
     assert bool((mask.sum(-1) >= min(topk, n_tiles)).all())
+
+
+@pytest.mark.parametrize("grid,tile", [((6, 8, 16), (6, 8, 8)), ((4, 4, 6), (2, 2, 3)), ((18, 48, 80), (6, 8, 8))])
+def test_tile_major_layout_change_is_exact(grid, tile):
+    from flex_block_attn_b200 import masks
+
+    S = grid[0] * grid[1] * grid[2]
+    B, Hn = (1, 2) if S > 10000 else (2, 3)
+    g = torch.Generator().manual_seed(S)
+    x = torch.randn((B, S, Hn, 128), generator=g).to(torch.bfloat16).cuda()
+    perm = masks.tile_major_permutation(grid, tile, device="cuda")
+    want = x.transpose(1, 2)[:, :, perm].contiguous()
+    got = masks.to_tile_major(x, grid, tile)
+    assert got.shape == (B, Hn, S, 128) and torch.equal(got, want)
+    back = masks.from_tile_major(got, grid, tile)
+    assert torch.equal(back, x)
