@@ -163,8 +163,19 @@ def cpu_sample_run(S: int, keep: float, n_qblocks: int, seed: int = 1234):
     return dt, int(mask.sum())
 
 
+def use_all_host_threads() -> int:
+    """torchrun pins OMP_NUM_THREADS=1; the CPU legs are meant to use every host core."""
+    n = os.cpu_count() or 1
+    try:
+        n = len(os.sched_getaffinity(0))
+    except (AttributeError, OSError):
+        pass
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def cpu_baseline(S: int, keep: float, target_s: float = 12.0):
-    threads = torch.get_num_threads()
+    threads = use_all_host_threads()
     cpu_sample_run(min(S, 3840), keep, 1)  # warm-up of the torch CPU kernels
     nq = 8 if S >= 8 * QB else max(1, S // QB)
     dt, pairs = cpu_sample_run(S, keep, nq)
@@ -183,7 +194,7 @@ def cpu_baseline(S: int, keep: float, target_s: float = 12.0):
 def run_reference_arm(args, rank, world):
     if rank != 0:
         return
-    threads = torch.get_num_threads()
+    threads = use_all_host_threads()
     times, pairs = [], 0
     for i in range(args.warmup + args.steps):
         dt, pairs = cpu_sample_run(args.seq, args.keep, 1, seed=1234 + i)
