@@ -14,18 +14,6 @@ namespace fba {
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
-__device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31u; }
-
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "elect.sync _|p, 0xffffffff;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(pred));
-    return pred != 0;
-}
-
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -133,18 +121,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
 // Bounded wait.  Every spin in these kernels goes through here: after `kWaitLimitCycles` SM
 // clocks without the phase completing (or as soon as another role of the CTA raised the abort
 // flag) the wait gives up, raises the CTA-wide abort flag and returns false; the caller then
@@ -161,24 +137,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         __nanosleep(FBA_SPIN_SLEEP_NS);
 #endif
         if (((++it) & 63u) == 0u) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitLimitCycles) {
-                *abort_flag = 1;
-                return false;
-            }
-        }
-    }
-}
-
-// Same contract as mbar_wait, but polls with the non-suspending test_wait: lower wake-up latency
-// at the price of issue slots, for the single-thread roles whose wake-up is on the critical path.
-__device__ __forceinline__ bool mbar_wait_hot(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_test_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    uint32_t it = 0;
-    while (true) {
-        if (mbar_test_wait(bar, parity)) return true;
-        if (((++it) & 1023u) == 0u) {
             if (*abort_flag) return false;
             if (clock64() - t0 > kWaitLimitCycles) {
                 *abort_flag = 1;
