@@ -149,3 +149,25 @@ def test_bad_inputs_raise():
         fba.flex_block_attn_func(q_nc, k, v, 128, 128, m)
     with pytest.raises(TypeError):
         fba.flex_block_attn_func(q, k, v, 128, 128, m.to(torch.uint8))
+
+
+def test_side_stream_and_second_device():
+    """The calls are ordered on the caller's current stream and follow the tensors' device."""
+    import flex_block_attn_b200 as fba
+
+    devices = ["cuda:0"] + (["cuda:1"] if torch.cuda.device_count() > 1 else [])
+    q, k, v, do = rand_qkv(1, 2, 2, 1536, 1536, seed=21)
+    mask = bernoulli_mask((1, 2, 4, 4), 0.5, 21)
+    want = orc.attention_slab(q.float(), k.float(), v.float(), mask, 384, 384, do.float())
+    for dev in devices:
+        side = torch.cuda.Stream(dev)
+        qd, kd, vd, dod, md = (t.to(dev) for t in (q, k, v, do, mask))
+        torch.cuda.synchronize(dev)
+        with torch.cuda.stream(side):
+            qq, kk, vv = (t.clone().requires_grad_() for t in (qd, kd, vd))
+            o = fba.flex_block_attn_func(qq, kk, vv, 384, 384, md)
+            o.backward(dod)
+        side.synchronize()
+        fba.check_status(torch.device(dev))
+        for g, w, nm in zip((o.detach(), qq.grad, kk.grad, vv.grad), (want[0], want[2], want[3], want[4]), ("O", "dQ", "dK", "dV")):
+            assert_close(g.float().cpu(), w, f"{dev} {nm}")
