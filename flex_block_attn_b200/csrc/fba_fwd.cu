@@ -38,6 +38,11 @@ constexpr uint32_t kFwdSmemBytes = kFwdSmemBars + 256 + 1024;  // + alignment sl
 #define FBA_FWD_POLY_PAIRS 0
 #endif
 
+// P is handed to the MMA issuer in this many pieces per 128-key step, so that O += P V starts while
+// the later exponentials are still being computed.
+constexpr int kFwdPieces = 4;
+constexpr int kFwdPiecePairs = 64 / kFwdPieces;   // bf16x2 words (= TMEM columns) per piece
+
 struct FwdParams {
     ListDev list;
     float* lse;
@@ -51,22 +56,22 @@ enum FwdBar : uint32_t {
     kBarRingFull = 2,                      // kFwdStages
     kBarRingEmpty = 2 + kFwdStages,        // kFwdStages
     kBarSFull = 2 + 2 * kFwdStages,        // 2
-    kBarPReady = 4 + 2 * kFwdStages,       // 2: P columns of keys 0-63 of the tile are in TMEM
-    kBarPHi = 6 + 2 * kFwdStages,          // 2: keys 64-127
-    kBarTurn = 8 + 2 * kFwdStages,         // 2: the other tile's issuer has issued its block
-    kBarODone = 10 + 2 * kFwdStages,       // 2
-    kBarCount = 12 + 2 * kFwdStages
+    kBarP = 4 + 2 * kFwdStages,            // 2 x 4: piece q of tile t's P is in TMEM (slot 4 t + q)
+    kBarTurn = 12 + 2 * kFwdStages,        // 2: the other tile's issuer has issued its block
+    kBarODone = 14 + 2 * kFwdStages,       // 2
+    kBarCount = 16 + 2 * kFwdStages
 };
 static_assert(8 * kBarCount + 16 <= 256, "barrier block overflows its 256-byte slot");
 static_assert(kFwdSmemBytes <= 232448, "exceeds the 227 KiB shared memory of an sm_100 CTA");
 
-// One half (4 k-steps = 64 keys) of O += P V.
-__device__ __forceinline__ void mma_pv_half(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_smem, int half,
-                                            bool accumulate) {
+// One piece (8 / kFwdPieces k-steps of 16 keys) of O += P V.
+__device__ __forceinline__ void mma_pv_piece(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_smem, int piece,
+                                             bool accumulate) {
     const uint32_t b = desc_lo_mnmajor(v_smem);
+    constexpr int kSteps = 8 / kFwdPieces;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const int kk = half * 4 + k;
+    for (int k = 0; k < kSteps; ++k) {
+        const int kk = piece * kSteps + k;
         umma_ts(d_tmem, p_tmem + static_cast<uint32_t>(kk) * 8u, b + kstep_mnmajor(kk), kIdescKM,
                 (accumulate || kk > 0) ? 1u : 0u);
     }
@@ -112,8 +117,7 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(bar(kBarSFull + t), 1);
-            mbar_init(bar(kBarPReady + t), 128);
-            mbar_init(bar(kBarPHi + t), 128);
+            for (int q = 0; q < kFwdPieces; ++q) mbar_init(bar(kBarP + 4 * t + q), 128);
             mbar_init(bar(kBarTurn + t), 1);
             mbar_init(bar(kBarODone + t), 1);
         }
@@ -243,7 +247,7 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     if (more) slot_k = wait_full(pos_k, 340 + t);
                     if (!ok) break;
                     if (i < 64) FBA_TRACE_REC(p.status, 1024 + i * 8 + t * 4 + 0);
-                    if (!mbar_wait(bar(kBarPReady + t), i & 1u, abort_flag)) {
+                    if (!mbar_wait(bar(kBarP + 4 * t), i & 1u, abort_flag)) {
                         report_timeout(p.status, 1, static_cast<uint32_t>(warp), i, 320 + t);
                         ok = false;
                         break;
@@ -259,14 +263,19 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     }
                     tc_fence_after();
                     if (i < 64) FBA_TRACE_REC(p.status, 1024 + i * 8 + t * 4 + 1);
-                    mma_pv_half(tO, tS, ring(slot_v), 0, i > 0);
-                    if (!mbar_wait(bar(kBarPHi + t), i & 1u, abort_flag)) {
-                        report_timeout(p.status, 1, static_cast<uint32_t>(warp), i, 325 + t);
-                        ok = false;
-                        break;
+                    mma_pv_piece(tO, tS, ring(slot_v), 0, i > 0);
+#pragma unroll
+                    for (int q = 1; q < kFwdPieces; ++q) {
+                        if (ok && !mbar_wait(bar(kBarP + 4 * t + q), i & 1u, abort_flag)) {
+                            report_timeout(p.status, 1, static_cast<uint32_t>(warp), i, 325 + t);
+                            ok = false;
+                        }
+                        if (ok) {
+                            tc_fence_after();
+                            mma_pv_piece(tO, tS, ring(slot_v), q, true);
+                        }
                     }
-                    tc_fence_after();
-                    mma_pv_half(tO, tS, ring(slot_v), 1, true);
+                    if (!ok) break;
                     if (more) {
                         mma_tile_kk(tS, sQt, ring(slot_k), false);
                         umma_commit(bar(kBarSFull + t));
@@ -331,15 +340,14 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     }
                 }
             }
-            float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+            // Row maximum: eight independent chains of two-input maxima.
+            float mm[8];
 #pragma unroll
-            for (int j = 0; j < 128; j += 8) {
-                m0 = max3(m0, __uint_as_float(u[j + 0]), __uint_as_float(u[j + 1]));
-                m1 = max3(m1, __uint_as_float(u[j + 2]), __uint_as_float(u[j + 3]));
-                m2 = max3(m2, __uint_as_float(u[j + 4]), __uint_as_float(u[j + 5]));
-                m3 = max3(m3, __uint_as_float(u[j + 6]), __uint_as_float(u[j + 7]));
-            }
-            const float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+            for (int j = 0; j < 8; ++j) mm[j] = __uint_as_float(u[j]);
+#pragma unroll
+            for (int j = 8; j < 128; ++j) mm[j & 7] = fmaxf(mm[j & 7], __uint_as_float(u[j]));
+            const float mx = fmaxf(fmaxf(fmaxf(mm[0], mm[1]), fmaxf(mm[2], mm[3])),
+                                   fmaxf(fmaxf(mm[4], mm[5]), fmaxf(mm[6], mm[7])));
             if (tracer && i < 64) FBA_TRACE_REC(p.status, i * 8 + t * 4 + 2);
 
             float alpha = 1.f;
@@ -371,39 +379,38 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             l2b.x *= alpha;
             l2b.y *= alpha;
             const float neg_off = have_off ? -off : 0.f;
-            // P goes to TMEM in two halves (keys 0-63, then 64-127) so that O += P V can start
-            // while the second half of the exponentials is still being computed.
+            // P goes to TMEM in pieces (keys in ascending order); a piece is announced to the
+            // issuer once its TMEM store has completed.
+            uint32_t pk[64];
 #pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                uint32_t pk[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int jj = 32 * hh + j;
-                    // (plain scalar fused multiply-adds: the packed f32x2 forms measured ~3 % slower here)
-                    float2 x;
-                    x.x = fmaf(__uint_as_float(u[2 * jj]), c, neg_off);
-                    x.y = fmaf(__uint_as_float(u[2 * jj + 1]), c, neg_off);
-                    float2 e;
-                    if ((j & 15) < FBA_FWD_POLY_PAIRS) {
-                        e = ex2_poly2(x);
-                    } else {
-                        e.x = ex2_approx(x.x);
-                        e.y = ex2_approx(x.y);
-                    }
-                    if (j & 1) {
-                        l2b.x += e.x;
-                        l2b.y += e.y;
-                    } else {
-                        l2a.x += e.x;
-                        l2a.y += e.y;
-                    }
-                    pk[j] = pack_bf16x2(e.x, e.y);
+            for (int j = 0; j < 64; ++j) {
+                // (plain scalar fused multiply-adds: the packed f32x2 forms measured ~3 % slower here)
+                float2 x;
+                x.x = fmaf(__uint_as_float(u[2 * j]), c, neg_off);
+                x.y = fmaf(__uint_as_float(u[2 * j + 1]), c, neg_off);
+                float2 e;
+                if ((j & 15) < FBA_FWD_POLY_PAIRS) {
+                    e = ex2_poly2(x);
+                } else {
+                    e.x = ex2_approx(x.x);
+                    e.y = ex2_approx(x.y);
                 }
-                tmem_st32(tS + 32u * hh, pk);
-                tmem_wait_st();
-                tc_fence_before();
-                mbar_arrive(bar((hh ? kBarPHi : kBarPReady) + t));
-                if (hh == 0 && tracer && i < 64) FBA_TRACE_REC(p.status, 3072 + i * 4 + t);
+                if (j & 1) {
+                    l2b.x += e.x;
+                    l2b.y += e.y;
+                } else {
+                    l2a.x += e.x;
+                    l2a.y += e.y;
+                }
+                pk[j] = pack_bf16x2(e.x, e.y);
+                if (j % kFwdPiecePairs == kFwdPiecePairs - 1) {
+                    const int q = j / kFwdPiecePairs;
+                    tmem_st16(tS + 16u * q, reinterpret_cast<uint32_t(&)[16]>(pk[16 * q]));
+                    tmem_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(bar(kBarP + 4 * t + q));
+                    if (q == 0 && tracer && i < 64) FBA_TRACE_REC(p.status, 3072 + i * 4 + t);
+                }
             }
             if (tracer && i < 64) FBA_TRACE_REC(p.status, i * 8 + t * 4 + 3);
         }

@@ -30,13 +30,6 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
 }
-
-// 3-input max (one instruction on sm_100).
-__device__ __forceinline__ float max3(float a, float b, float c) {
-    float d;
-    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-    return d;
-}
 // Packed fp32 pairs (sm_100 executes these as one instruction on a 64-bit register pair).
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
     float2 d;
