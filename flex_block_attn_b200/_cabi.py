@@ -26,8 +26,10 @@ EXPORTED_SYMBOLS = (
     "fba_ssta_index",
     "fba_tile_major",
     "fba_fwd",
+    "fba_fwd_scaled",
     "fba_bwd_scratch_bytes",
     "fba_bwd",
+    "fba_bwd_scaled",
     "fba_bwd_static_scratch_max_rows",
     "fba_bwd_static_scratch",
 )
@@ -86,10 +88,15 @@ def lib() -> ctypes.CDLL:
     L.fba_tile_major.argtypes = [vp, vp] + [i32] * 9 + [vp]
     L.fba_fwd.restype = i32
     L.fba_fwd.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, ctypes.POINTER(FbaList), vp, vp]
+    L.fba_fwd_scaled.restype = i32
+    L.fba_fwd_scaled.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, ctypes.POINTER(FbaList),
+                                 ctypes.c_float, vp, vp]
     L.fba_bwd_scratch_bytes.restype = i32
     L.fba_bwd_scratch_bytes.argtypes = [i32, i32, i32, ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]
     L.fba_bwd.restype = i32
     L.fba_bwd.argtypes = [vp] * 9 + [i32] * 5 + [ctypes.POINTER(FbaList), vp, vp, vp, vp]
+    L.fba_bwd_scaled.restype = i32
+    L.fba_bwd_scaled.argtypes = [vp] * 9 + [i32] * 5 + [ctypes.POINTER(FbaList), ctypes.c_float, vp, vp, vp, vp]
     L.fba_bwd_static_scratch_max_rows.restype = ctypes.c_uint64
     L.fba_bwd_static_scratch_max_rows.argtypes = []
     L.fba_bwd_static_scratch.restype = i32

@@ -1,7 +1,7 @@
 // Block-sparse attention backward for sm_100a.
 //
 // Three kernels, in stream order:
-//   1. bwd_prep_kernel      per row (-LSE * log2 e, -sum_d dO * O / sqrt(128)); the counterpart of
+//   1. bwd_prep_kernel      per row (-LSE * log2 e, -scale * sum_d dO * O); the counterpart of
 //                           the reference's bwd_attend_prep_ker (flex_block_attn_h100.cu:339-389).
 //                           HBM-bound, one pass over O and dO.
 //   2. fba_bwd_kernel       key-major main kernel, the counterpart of bwd_attend_ker (.cu:572-802).
@@ -72,10 +72,11 @@ static_assert(kBwdSmemBytes <= 232448, "exceeds the 227 KiB shared memory of an 
 
 struct BwdParams {
     ListDev list;          // key-major: rows = key tiles / rows_div, entries = query tiles / sub
-    const float2* ld;      // [B*Hq, nMt, 2, 128]: per query tile 128 x (-lse*log2e), then 128 x (-delta/sqrt(128))
+    const float2* ld;      // [B*Hq, nMt, 2, 128]: per query tile 128 x (-lse*log2e), then 128 x (-delta*scale)
     float* dq_accum;       // [B*Hq, nMt, 4 column chunks, 4 row groups, 8, 32, 4] fp32
     uint32_t* status;
     int n_mtiles, Hq, Hkv;
+    float scale;           // softmax scale
 };
 
 // ------------------------------------------------------------------------------------------
@@ -83,13 +84,13 @@ __global__ void __launch_bounds__(256) bwd_prep_kernel(const __nv_bfloat16* __re
                                                       const __nv_bfloat16* __restrict__ dout,
                                                       const float* __restrict__ lse,
                                                       float2* __restrict__ ld, int Sq, int rows_pad,
-                                                      long long total_rows) {
+                                                      long long total_rows, float scale) {
     const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     if (w >= total_rows) return;
     const int lane = threadIdx.x & 31;
     const long long bh = w / rows_pad;
     const int r = static_cast<int>(w % rows_pad);
-    // Output layout, per 128-row query tile: 128 x (-lse2) followed by 128 x (-delta / sqrt(128)),
+    // Output layout, per 128-row query tile: 128 x (-lse2) followed by 128 x (-delta * scale),
     // so the main kernel fetches four columns' worth of either quantity with one 16-byte
     // shared-memory read and feeds it straight into packed fused multiply-adds.
     float neg_lse2 = -INFINITY, neg_delta_s = 0.f;
@@ -113,7 +114,7 @@ __global__ void __launch_bounds__(256) bwd_prep_kernel(const __nv_bfloat16* __re
         // A row that attended to nothing has LSE = -inf; -inf here makes every P of it exactly 0
         // (exp2(s * c - inf)), and so its dS.
         neg_lse2 = l == -INFINITY ? -INFINITY : -l * kLog2e;
-        neg_delta_s = -s * kSoftmaxScale;
+        neg_delta_s = -s * scale;
     }
     if (lane == 0) {
         float* out = reinterpret_cast<float*>(ld) + (w >> 7) * 256 + (w & 127);
@@ -465,7 +466,8 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const int quad = warp & 3;
         const int row = quad * 32 + lane;  // key row inside the tile == TMEM lane
         const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
-        const float c = kSoftmaxScale * kLog2e;
+        const float c = p.scale * kLog2e;
+        const float2 sc2 = make_float2(p.scale, p.scale);
         const int mbit0 = 8 * (row >> 6);  // key-half part of the mask bit index
         int it = 0;
         bool ok = true;
@@ -543,11 +545,11 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
                         for (int j = 0; j < 2; ++j) {
                             const int col = 8 * q8 + 4 * j;
-                            const float4 d4 = del4[col >> 2];   // -delta/sqrt(128) of columns col .. col+3
+                            const float4 d4 = del4[col >> 2];   // -delta*scale of columns col .. col+3
                             const float2 t0 = fma2(make_float2(__uint_as_float(dp[col]), __uint_as_float(dp[col + 1])),
-                                                   make_float2(kSoftmaxScale, kSoftmaxScale), make_float2(d4.x, d4.y));
+                                                   sc2, make_float2(d4.x, d4.y));
                             const float2 t1 = fma2(make_float2(__uint_as_float(dp[col + 2]), __uint_as_float(dp[col + 3])),
-                                                   make_float2(kSoftmaxScale, kSoftmaxScale), make_float2(d4.z, d4.w));
+                                                   sc2, make_float2(d4.z, d4.w));
                             const float2 e0 = mul2(make_float2(pr[col], pr[col + 1]), t0);
                             const float2 e1 = mul2(make_float2(pr[col + 2], pr[col + 3]), t1);
                             wds[2 * j] = pack_bf16x2(e0.x, e0.y);
@@ -635,13 +637,15 @@ extern "C" int fba_bwd_scratch_bytes(int B, int Hq, int Sq, uint64_t* lse_delta_
     return FBA_OK;
 }
 
-extern "C" int fba_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse,
-                       const void* dout, void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int Sq,
-                       int Skv, const fba_list_t* k2q, float* lse_delta, float* dq_accum,
-                       uint32_t* status, void* stream_) {
+extern "C" int fba_bwd_scaled(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                              const void* dout, void* dq, void* dk, void* dv, int B, int Hq, int Hkv,
+                              int Sq, int Skv, const fba_list_t* k2q, float softmax_scale, float* lse_delta,
+                              float* dq_accum, uint32_t* status, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (!q || !k || !v || !o || !lse || !dout || !dq || !dk || !dv || !lse_delta || !dq_accum || !status)
         return set_error(FBA_ERR_BAD_ARG, "fba_bwd: null pointer argument");
+    if (!(softmax_scale > 0.f) || !(softmax_scale < INFINITY))
+        return set_error(FBA_ERR_BAD_ARG, "fba_bwd: softmax_scale must be positive and finite");
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || Sq <= 0 || Skv <= 0)
         return set_error(FBA_ERR_BAD_ARG, "fba_bwd: non-positive size");
     if (Hq % Hkv != 0) return set_error(FBA_ERR_BAD_ARG, "fba_bwd: Hq must be a multiple of Hkv");
@@ -675,7 +679,7 @@ extern "C" int fba_bwd(const void* q, const void* k, const void* v, const void* 
         const long long blocks = (total_rows * 32 + 255) / 256;
         bwd_prep_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
             static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dout), lse,
-            reinterpret_cast<float2*>(lse_delta), Sq, rows_pad, total_rows);
+            reinterpret_cast<float2*>(lse_delta), Sq, rows_pad, total_rows, softmax_scale);
         if ((rc = check_launch("bwd_prep_kernel")) != FBA_OK) return rc;
     }
     if (cudaMemsetAsync(dq_accum, 0, static_cast<size_t>(total_rows) * 128 * sizeof(float), stream) != cudaSuccess) {
@@ -697,6 +701,7 @@ extern "C" int fba_bwd(const void* q, const void* k, const void* v, const void* 
         p.n_mtiles = n_mtiles;
         p.Hq = Hq;
         p.Hkv = Hkv;
+        p.scale = softmax_scale;
         dim3 grid(n_ntiles, static_cast<unsigned>(n_bhk));
         timing_mark(2, true, stream);
         fba_bwd_kernel<<<grid, kBwdThreads, kBwdSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv, p);
@@ -710,6 +715,14 @@ extern "C" int fba_bwd(const void* q, const void* k, const void* v, const void* 
         if ((rc = check_launch("bwd_dq_convert_kernel")) != FBA_OK) return rc;
     }
     return FBA_OK;
+}
+
+extern "C" int fba_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                       const void* dout, void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int Sq,
+                       int Skv, const fba_list_t* k2q, float* lse_delta, float* dq_accum,
+                       uint32_t* status, void* stream) {
+    return fba_bwd_scaled(q, k, v, o, lse, dout, dq, dk, dv, B, Hq, Hkv, Sq, Skv, k2q, kSoftmaxScale, lse_delta,
+                          dq_accum, status, stream);
 }
 
 // ------------------------------------------------------------------------------------------

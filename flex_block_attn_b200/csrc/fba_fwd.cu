@@ -45,9 +45,10 @@ constexpr int kFwdPiecePairs = 64 / kFwdPieces;   // bf16x2 words (= TMEM column
 
 struct FwdParams {
     ListDev list;
-    float* lse;
+    float* lse;            // may be null: no log-sum-exp is written (inference)
     uint32_t* status;
     int n_mtiles, Sq, Hq, Hkv;
+    float scale_log2;      // softmax scale * log2(e)
 };
 
 // Barrier slots (8 bytes each) inside the barrier block.
@@ -304,7 +305,7 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const long long lrow = t ? lrow1 : lrow0;
         const uint32_t sQt = t ? sQ1 : sQ0;
         const bool tile_valid = mt < p.n_mtiles;
-        const float c = kSoftmaxScale * kLog2e;
+        const float c = p.scale_log2;
         const int g = row >> 4;
         const bool tracer = (warp & 3) == 0 && lane == 0;
 
@@ -454,7 +455,7 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     }
                 }
                 const int grow = mt * 128 + row;
-                if (grow < p.Sq)
+                if (p.lse != nullptr && grow < p.Sq)
                     p.lse[static_cast<long long>(bh) * p.Sq + grow] =
                         l > 0.f ? (off + lg2_approx(l)) * kLn2 : -INFINITY;
                 fence_proxy_async_smem();
@@ -489,12 +490,14 @@ static int check_list(const fba_list_t* l, const char* who) {
     return FBA_OK;
 }
 
-extern "C" int fba_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Hq,
-                       int Hkv, int Sq, int Skv, const fba_list_t* q2k, uint32_t* status,
-                       void* stream_) {
+static int fwd_impl(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Hq,
+                    int Hkv, int Sq, int Skv, const fba_list_t* q2k, float softmax_scale, uint32_t* status,
+                    void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    if (!q || !k || !v || !o || !lse || !status)
+    if (!q || !k || !v || !o || !status)
         return set_error(FBA_ERR_BAD_ARG, "fba_fwd: null pointer argument");
+    if (!(softmax_scale > 0.f) || !(softmax_scale < INFINITY))
+        return set_error(FBA_ERR_BAD_ARG, "fba_fwd: softmax_scale must be positive and finite");
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || Sq <= 0 || Skv <= 0)
         return set_error(FBA_ERR_BAD_ARG, "fba_fwd: non-positive size");
     if (Hq % Hkv != 0) return set_error(FBA_ERR_BAD_ARG, "fba_fwd: Hq must be a multiple of Hkv");
@@ -533,10 +536,23 @@ extern "C" int fba_fwd(const void* q, const void* k, const void* v, void* o, flo
     p.Sq = Sq;
     p.Hq = Hq;
     p.Hkv = Hkv;
+    p.scale_log2 = softmax_scale * kLog2e;
     dim3 grid((n_mtiles + 1) / 2, B * Hq);
     timing_mark(1, true, stream);
     fba_fwd_kernel<<<grid, kFwdThreads, kFwdSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, p);
     rc = check_launch("fba_fwd_kernel");
     timing_mark(1, false, stream);
     return rc;
+}
+
+extern "C" int fba_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Hq,
+                       int Hkv, int Sq, int Skv, const fba_list_t* q2k, uint32_t* status, void* stream) {
+    if (!lse) return set_error(FBA_ERR_BAD_ARG, "fba_fwd: null pointer argument");
+    return fwd_impl(q, k, v, o, lse, B, Hq, Hkv, Sq, Skv, q2k, kSoftmaxScale, status, stream);
+}
+
+extern "C" int fba_fwd_scaled(const void* q, const void* k, const void* v, void* o, float* lse, int B,
+                              int Hq, int Hkv, int Sq, int Skv, const fba_list_t* q2k,
+                              float softmax_scale, uint32_t* status, void* stream) {
+    return fwd_impl(q, k, v, o, lse, B, Hq, Hkv, Sq, Skv, q2k, softmax_scale, status, stream);
 }

@@ -19,6 +19,7 @@ Differences that a caller can observe:
 from __future__ import annotations
 
 import ctypes
+import math
 import os
 from dataclasses import dataclass
 from typing import Optional
@@ -275,26 +276,41 @@ def _check_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
         raise RuntimeError("q, k and v must be on the same device")
 
 
-def forward_with_lists(q, k, v, lists: SparseLists):
-    """Run the forward kernel; returns (o bf16 [B,H,Sq,128], lse fp32 [B,H,Sq])."""
+def _scale_of(softmax_scale) -> float:
+    if softmax_scale is None:
+        return 1.0 / math.sqrt(HEAD_DIM)
+    softmax_scale = float(softmax_scale)
+    if not (softmax_scale > 0.0 and math.isfinite(softmax_scale)):
+        raise ValueError("softmax_scale must be positive and finite")
+    return softmax_scale
+
+
+def forward_with_lists(q, k, v, lists: SparseLists, softmax_scale=None, need_lse: bool = True):
+    """Run the forward kernel; returns (o bf16 [B,H,Sq,128], lse fp32 [B,H,Sq]).
+
+    ``softmax_scale`` (default 1/sqrt(128), the reference's fixed value) multiplies q k^T before the
+    softmax.  With ``need_lse=False`` (inference) no log-sum-exp is written and ``lse`` is None.
+    """
     _check_qkv(q, k, v)
     B, Hq, Sq, _ = q.shape
     Hkv, Skv = k.shape[1], k.shape[2]
     dev = q.device
     o = torch.empty_like(q)
-    lse = torch.empty((B, Hq, Sq), dtype=torch.float32, device=dev)
+    lse = torch.empty((B, Hq, Sq), dtype=torch.float32, device=dev) if need_lse else None
     lst = lists.fwd_list()
     with torch.cuda.device(dev):
-        rc = _cabi.lib().fba_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
-                                 B, Hq, Hkv, Sq, Skv, ctypes.byref(lst), _status(dev).data_ptr(),
-                                 _stream_ptr(dev))
-    _cabi.check(rc, "fba_fwd")
+        rc = _cabi.lib().fba_fwd_scaled(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                        lse.data_ptr() if need_lse else None, B, Hq, Hkv, Sq, Skv,
+                                        ctypes.byref(lst), _scale_of(softmax_scale), _status(dev).data_ptr(),
+                                        _stream_ptr(dev))
+    _cabi.check(rc, "fba_fwd_scaled")
     _maybe_check(dev)
     return o, lse
 
 
-def backward_with_lists(q, k, v, o, lse, dout, lists: SparseLists):
-    """Run the backward kernels; returns (dq, dk, dv) in bf16."""
+def backward_with_lists(q, k, v, o, lse, dout, lists: SparseLists, softmax_scale=None):
+    """Run the backward kernels; returns (dq, dk, dv) in bf16.  ``softmax_scale`` must be the
+    forward's."""
     _check_qkv(q, k, v)
     B, Hq, Sq, _ = q.shape
     Hkv, Skv = k.shape[1], k.shape[2]
@@ -316,11 +332,12 @@ def backward_with_lists(q, k, v, o, lse, dout, lists: SparseLists):
     dq_accum = torch.empty((n2.value // 4,), dtype=torch.float32, device=dev)
     lst = lists.bwd_list()
     with torch.cuda.device(dev):
-        rc = _cabi.lib().fba_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
-                                 dout.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                                 B, Hq, Hkv, Sq, Skv, ctypes.byref(lst), lse_delta.data_ptr(),
-                                 dq_accum.data_ptr(), _status(dev).data_ptr(), _stream_ptr(dev))
-    _cabi.check(rc, "fba_bwd")
+        rc = _cabi.lib().fba_bwd_scaled(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                        dout.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                        B, Hq, Hkv, Sq, Skv, ctypes.byref(lst), _scale_of(softmax_scale),
+                                        lse_delta.data_ptr(), dq_accum.data_ptr(), _status(dev).data_ptr(),
+                                        _stream_ptr(dev))
+    _cabi.check(rc, "fba_bwd_scaled")
     _maybe_check(dev)
     return dq, dk, dv
 
@@ -358,7 +375,7 @@ def _flex_block_attn_backward(q, k, v, o, lse, do, q_block_size, kv_block_size, 
 
 class FlexBlockAttnFunc(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, q_block_size, kv_block_size, block_mask, is_grad_enabled):
+    def forward(ctx, q, k, v, q_block_size, kv_block_size, block_mask, is_grad_enabled, softmax_scale=None):
         assert q_block_size % 16 == 0, f"q_block_size ({q_block_size}) must be divisible by 16"
         assert kv_block_size % 64 == 0, f"kv_block_size ({kv_block_size}) must be divisible by 64"
         assert kv_block_size % q_block_size == 0 or q_block_size % kv_block_size == 0, \
@@ -392,20 +409,21 @@ class FlexBlockAttnFunc(torch.autograd.Function):
             assert not is_grad or lists.bwd_idx is not None, "these lists were built without the key-major direction"
         else:
             lists = build_lists(block_mask, q_block_size, kv_block_size, q_seq_len, kv_seq_len, need_bwd=is_grad)
-        o, lse = forward_with_lists(q, k, v, lists)
+        o, lse = forward_with_lists(q, k, v, lists, softmax_scale, need_lse=is_grad)
         if is_grad:
             ctx.save_for_backward(q, k, v, o, lse)
             ctx.lists = lists
+            ctx.softmax_scale = softmax_scale
         return o
 
     @staticmethod
     def backward(ctx, dout, *args):
         q, k, v, o, lse = ctx.saved_tensors
-        dq, dk, dv = backward_with_lists(q, k, v, o, lse, dout, ctx.lists)
-        return dq, dk, dv, None, None, None, None
+        dq, dk, dv = backward_with_lists(q, k, v, o, lse, dout, ctx.lists, ctx.softmax_scale)
+        return dq, dk, dv, None, None, None, None, None
 
 
-def flex_block_attn_func(q, k, v, q_block_size, kv_block_size, block_mask):
+def flex_block_attn_func(q, k, v, q_block_size, kv_block_size, block_mask, softmax_scale=None):
     """Block-sparse attention, drop-in for the reference's function of the same name.
 
     Args:
@@ -417,8 +435,12 @@ def flex_block_attn_func(q, k, v, q_block_size, kv_block_size, block_mask):
             [batch, heads, ...same...]; True = the query block attends to the key block.
             (Extension: a ``SparseLists`` from ``build_lists`` / ``sta_lists`` / ``ssta_lists`` is
             accepted in its place and skips the compaction.)
+        softmax_scale: extension, not in the reference (which fixes 1/sqrt(128)): factor applied
+            to q k^T before the softmax; None = 1/sqrt(128).  Without grad mode (inference) the
+            forward also skips writing the log-sum-exp.
 
     Returns:
         [batch, heads, q_seq_len, 128] bf16; differentiable w.r.t. q, k and v.
     """
-    return FlexBlockAttnFunc.apply(q, k, v, q_block_size, kv_block_size, block_mask, torch.is_grad_enabled())
+    return FlexBlockAttnFunc.apply(q, k, v, q_block_size, kv_block_size, block_mask, torch.is_grad_enabled(),
+                                   softmax_scale)

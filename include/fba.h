@@ -145,6 +145,15 @@ int fba_tile_major(const void* src, void* dst, int B, int Hn, int T, int H, int 
  */
 int fba_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Hq,
             int Hkv, int Sq, int Skv, const fba_list_t* q2k, uint32_t* status, void* stream);
+/*
+ * fba_fwd with a caller-chosen softmax scale (no counterpart in the reference, whose kernels fix
+ * 1/sqrt(128), flex_block_attn_h100.cu:201): scores are softmax_scale * q k^T; softmax_scale
+ * must be positive and finite.  lse may be NULL: then no log-sum-exp is written (inference-only
+ * forward).  fba_fwd(...) == fba_fwd_scaled(..., 1/sqrt(128), ...) with lse required.
+ */
+int fba_fwd_scaled(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Hq,
+                   int Hkv, int Sq, int Skv, const fba_list_t* q2k, float softmax_scale,
+                   uint32_t* status, void* stream);
 
 /*
  * Backward (replaces attention_backward, reference .cu:1009-1267, bwd_attend_prep_ker .cu:339-389
@@ -160,6 +169,11 @@ int fba_bwd(const void* q, const void* k, const void* v, const void* o, const fl
             const void* dout, void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int Sq,
             int Skv, const fba_list_t* k2q, float* lse_delta, float* dq_accum, uint32_t* status,
             void* stream);
+/* fba_bwd for a forward that ran with fba_fwd_scaled: pass the same softmax_scale. */
+int fba_bwd_scaled(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                   const void* dout, void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int Sq,
+                   int Skv, const fba_list_t* k2q, float softmax_scale, float* lse_delta,
+                   float* dq_accum, uint32_t* status, void* stream);
 
 /*
  * Backward for callers that cannot allocate device memory (no counterpart in the reference, whose

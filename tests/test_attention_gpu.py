@@ -171,3 +171,49 @@ def test_side_stream_and_second_device():
         fba.check_status(torch.device(dev))
         for g, w, nm in zip((o.detach(), qq.grad, kk.grad, vv.grad), (want[0], want[2], want[3], want[4]), ("O", "dQ", "dK", "dV")):
             assert_close(g.float().cpu(), w, f"{dev} {nm}")
+
+
+@pytest.mark.parametrize("scale", [0.05, 1.0 / 128 ** 0.5, 0.2])
+@pytest.mark.parametrize("qb,kb", [(384, 384), (64, 192)])
+def test_softmax_scale_argument(scale, qb, kb):
+    """softmax_scale (not in the reference, which fixes 1/sqrt(128)): O, LSE and all three gradients
+    against the oracle evaluated with the same scale, on both the aligned and the tile-mask path."""
+    import flex_block_attn_b200 as fba
+
+    S = 1536
+    q, k, v, do = rand_qkv(1, 4, 2, S, S, seed=21, device="cuda")
+    mask = bernoulli_mask((1, 4, S // qb, S // kb), 0.5, 21).cuda()
+    q1, k1, v1 = (t.clone().requires_grad_() for t in (q, k, v))
+    o = fba.flex_block_attn_func(q1, k1, v1, qb, kb, mask, softmax_scale=scale)
+    o.backward(do)
+    fba.check_status()
+    want = orc.attention_slab(q.float(), k.float(), v.float(), mask, qb, kb, do.float(), softmax_scale=scale)
+    for g, w, nm in zip((o.detach(), q1.grad, k1.grad, v1.grad), (want[0], want[2], want[3], want[4]),
+                        ("O", "dQ", "dK", "dV")):
+        assert_close(g.float(), w, f"scale {scale} {nm}")
+    lists = fba.build_lists(mask, qb, kb, S, S, need_bwd=False)
+    _, lse = fba.forward_with_lists(q, k, v, lists, softmax_scale=scale)
+    assert torch.allclose(lse, want[1], atol=2e-3, rtol=1e-4)
+    if abs(scale - 1.0 / 128 ** 0.5) < 1e-9:
+        # the default and the explicit reference value are the same computation
+        o0 = fba.flex_block_attn_func(q, k, v, qb, kb, mask)
+        assert torch.equal(o0, o.detach())
+
+
+def test_inference_forward_skips_lse():
+    """Without grad mode the forward writes no log-sum-exp; O is bit-identical to the training
+    forward's."""
+    import flex_block_attn_b200 as fba
+
+    q, k, v, _ = rand_qkv(2, 2, 2, 768, 768, seed=22, device="cuda")
+    mask = bernoulli_mask((2, 2, 2, 2), 0.5, 22).cuda()
+    lists = fba.build_lists(mask, 384, 384, 768, 768, need_bwd=False)
+    o_train, lse = fba.forward_with_lists(q, k, v, lists)
+    o_inf, none = fba.forward_with_lists(q, k, v, lists, need_lse=False)
+    assert none is None and lse is not None
+    assert torch.equal(o_train, o_inf)
+    with torch.no_grad():
+        o_api = fba.flex_block_attn_func(q, k, v, 384, 384, mask)
+    assert torch.equal(o_api, o_train)
+    with pytest.raises(ValueError):
+        fba.flex_block_attn_func(q, k, v, 384, 384, mask, softmax_scale=-1.0)

@@ -43,6 +43,23 @@ def test_config1_explicit_slab_sdpa_agree():
         assert torch.allclose(dv, vr.grad, atol=2e-5, rtol=1e-4)
 
 
+def test_softmax_scale_explicit_slab_sdpa_agree():
+    """The optional softmax_scale of the three oracle forms means the same thing (SDPA's ``scale``)."""
+    q, k, v, do = rand_qkv(1, 2, 1, 768, 768, seed=3, dtype=torch.float32)
+    mask = bernoulli_mask((1, 2, 6, 6), 0.5, seed=3)
+    qr, kr, vr = (t.clone().requires_grad_() for t in (q, k, v))
+    o_ref = orc.sdpa_dense(qr, kr, vr, mask, 128, 128, softmax_scale=0.2)
+    o_ref.backward(do)
+    for fn in (orc.attention_explicit, orc.attention_slab):
+        o, lse, dq, dk, dv = fn(q, k, v, mask, 128, 128, do, softmax_scale=0.2)
+        assert torch.allclose(o, o_ref, atol=1e-5, rtol=1e-4)
+        assert torch.allclose(dq, qr.grad, atol=5e-5, rtol=1e-4)
+        assert torch.allclose(dk, kr.grad, atol=5e-5, rtol=1e-4)
+        assert torch.allclose(dv, vr.grad, atol=5e-5, rtol=1e-4)
+    o_default = orc.attention_slab(q, k, v, mask, 128, 128)[0]
+    assert not torch.allclose(o_default, o_ref, atol=1e-3)
+
+
 def test_gqa_4d_mask_and_asymmetric_blocks():
     q, k, v, do = rand_qkv(2, 4, 2, 256, 384, seed=3, dtype=torch.float32)
     mask = bernoulli_mask((2, 4, 256 // 32, 384 // 128), 0.5, seed=4)
