@@ -32,6 +32,12 @@ EXPORTED_SYMBOLS = (
     "fba_bwd_scaled",
     "fba_bwd_static_scratch_max_rows",
     "fba_bwd_static_scratch",
+    "fba_peer_alloc",
+    "fba_peer_free",
+    "fba_peer_export",
+    "fba_peer_open",
+    "fba_peer_close",
+    "fba_peer_exchange",
 )
 
 
@@ -101,6 +107,18 @@ def lib() -> ctypes.CDLL:
     L.fba_bwd_static_scratch_max_rows.argtypes = []
     L.fba_bwd_static_scratch.restype = i32
     L.fba_bwd_static_scratch.argtypes = [vp] * 9 + [i32] * 5 + [ctypes.POINTER(FbaList), vp, vp]
+    L.fba_peer_alloc.restype = i32
+    L.fba_peer_alloc.argtypes = [ctypes.c_uint64, ctypes.POINTER(vp)]
+    L.fba_peer_free.restype = i32
+    L.fba_peer_free.argtypes = [vp]
+    L.fba_peer_export.restype = i32
+    L.fba_peer_export.argtypes = [vp, ctypes.c_char_p]
+    L.fba_peer_open.restype = i32
+    L.fba_peer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
+    L.fba_peer_close.restype = i32
+    L.fba_peer_close.argtypes = [vp]
+    L.fba_peer_exchange.restype = i32
+    L.fba_peer_exchange.argtypes = [vp, ctypes.POINTER(vp)] + [i32] * 11 + [vp]
     if L.fba_abi_version() != 1:
         raise RuntimeError("libfba_b200.so has an unexpected ABI version")
     _LIB = L

@@ -12,6 +12,9 @@ traffic, reference flex_block_attn_h100.cu:924), so every (batch, head) is an in
     (no pack / unpack pass); over NCCL the group runs as one fused all-to-all on NVLink.
   * ``ulysses_flex_block_attn``: all-to-all in, block-sparse attention on the local heads,
     all-to-all out, differentiable end to end.
+  * ``PeerExchange``: the same exchange for activations held as [B, S/P, H, D] in raster token
+    order, fused with the transpose and the raster <-> tile-major token reorder: one kernel per
+    GPU stores every row into its final place in the owning GPU's buffer over NVLink peer memory.
 """
 from __future__ import annotations
 
@@ -129,3 +132,162 @@ def ulysses_flex_block_attn(q, k, v, q_block_size, kv_block_size, mask_fn: Calla
         mask = mask_fn(qh, kh)
     oh = attn_fn(qh, kh, vh, q_block_size, kv_block_size, mask)
     return _HeadToSeq.apply(oh, group)
+
+
+# ---------------------------------------------------------------------------------------------
+# Exchange fused with the layout change, over peer memory.
+# ---------------------------------------------------------------------------------------------
+def peer_exchange_rows(rank: int, world: int, B: int, H: int, grid, tile, to_head: bool):
+    """Where ``fba_peer_exchange`` puts every 128-element row of rank ``rank``'s source tensor.
+
+    Plain-torch statement of the kernel's index arithmetic (CPU; used by the tests and as the
+    definition of the layouts): returns ``(dest_rank, dest_row)``, one entry per source row in
+    source order.  ``to_head``: source [B, S/P, H] raster chunk -> [B, H/P, S] tile-major on the
+    rank owning the head; otherwise source [B, H/P, S] tile-major -> [B, S/P, H] raster chunk on
+    the rank owning the token.
+    """
+    from .masks import tile_major_permutation
+
+    T, Hh, W = grid
+    S = T * Hh * W
+    if H % world or S % world:
+        raise ValueError("heads and sequence must divide over the ranks")
+    Hl, Sl = H // world, S // world
+    perm = tile_major_permutation(grid, tile)          # perm[tile_major_pos] = raster_pos
+    inv = torch.argsort(perm)                          # inv[raster_pos] = tile_major_pos
+    if to_head:
+        b, sl, h = torch.meshgrid(torch.arange(B), torch.arange(Sl), torch.arange(H), indexing="ij")
+        dest = h // Hl
+        row = (b * Hl + (h - dest * Hl)) * S + inv[rank * Sl + sl]
+    else:
+        b, hl, s = torch.meshgrid(torch.arange(B), torch.arange(Hl), torch.arange(S), indexing="ij")
+        r = perm[s]
+        dest = r // Sl
+        row = (b * Sl + (r - dest * Sl)) * H + rank * Hl + hl
+    return dest.reshape(-1), row.reshape(-1)
+
+
+class _RawDeviceMemory:
+    """Device memory owned elsewhere, exposed to torch through the CUDA array interface."""
+
+    def __init__(self, ptr: int, n_elems: int):
+        self.__cuda_array_interface__ = {"shape": (n_elems,), "typestr": "<i2", "data": (ptr, False),
+                                         "version": 2, "strides": None}
+
+
+class PeerExchange:
+    """Sequence <-> head exchange fused with the raster <-> tile-major token reorder.
+
+    Every rank holds ``[B, S/P, H, 128]`` (bf16, raster (t, h, w) token order, its contiguous
+    chunk of the sequence) and needs ``[B, H/P, S, 128]`` for its heads with tokens in tile-major
+    order.  One kernel per rank stores each row straight into its final place in the owning
+    rank's buffer over NVLink (``fba_peer_exchange``); there is no pack, unpack, transpose or
+    permutation pass on either side.  NCCL is used only for two one-element all-reduces that
+    order the stores against the readers on the other GPUs.
+
+    The destination buffers (``slots`` per direction, so that q, k and v can be in flight
+    together) are allocated once and shared through CUDA IPC.  The tensors returned by
+    ``seq_to_head`` / ``head_to_seq`` ALIAS those buffers: they stay valid until the next call
+    with the same slot and direction.  Collective: every rank of ``group`` must make the same
+    calls in the same order.  Call ``close()`` (collective) when done.
+    """
+
+    def __init__(self, B: int, H: int, grid, tile=(1, 1, 1), group=None, device=None, slots: int = 1):
+        import ctypes
+
+        from . import _cabi
+
+        self._lib = _cabi.lib()
+        self._check = _cabi.check
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.B, self.H, self.grid, self.tile = B, H, tuple(grid), tuple(tile)
+        T, Hh, W = self.grid
+        self.S = T * Hh * W
+        if H % self.world or self.S % self.world:
+            raise ValueError("heads and sequence must divide over the ranks")
+        if self.world > 16:
+            raise ValueError("at most 16 ranks")
+        self.Hl, self.Sl = H // self.world, self.S // self.world
+        self._n_elems = B * self.Hl * self.S * 128          # same count for both layouts
+        self.slots = slots
+        self._own, self._peer_ptrs, self._opened = [], [], []
+        self._closed = False
+        handles = []
+        with torch.cuda.device(self.device):
+            for _ in range(2 * slots):                       # [to_head slots..., to_seq slots...]
+                p = ctypes.c_void_p()
+                self._check(self._lib.fba_peer_alloc(self._n_elems * 2, ctypes.byref(p)), "fba_peer_alloc")
+                self._own.append(p.value)
+                h = ctypes.create_string_buffer(64)
+                self._check(self._lib.fba_peer_export(p.value, h), "fba_peer_export")
+                handles.append(h.raw)
+            gathered = [None] * self.world
+            dist.all_gather_object(gathered, handles, group=group)
+            for i in range(2 * slots):
+                ptrs = (ctypes.c_void_p * self.world)()
+                for r in range(self.world):
+                    if r == self.rank:
+                        ptrs[r] = self._own[i]
+                    else:
+                        p = ctypes.c_void_p()
+                        self._check(self._lib.fba_peer_open(gathered[r][i], ctypes.byref(p)), "fba_peer_open")
+                        self._opened.append(p.value)
+                        ptrs[r] = p.value
+                self._peer_ptrs.append(ptrs)
+            self._flag = torch.zeros(1, device=self.device)
+            self._views = [torch.as_tensor(_RawDeviceMemory(p, self._n_elems), device=self.device).view(torch.bfloat16)
+                           for p in self._own]
+        self._barrier()
+
+    def _barrier(self):
+        # stream-ordered on every rank: completes only after all ranks' earlier work on their
+        # current streams has completed
+        dist.all_reduce(self._flag, group=self.group)
+
+    def _run(self, x, to_head: bool, slot: int):
+        if self._closed:
+            raise RuntimeError("PeerExchange is closed")
+        if not 0 <= slot < self.slots:
+            raise ValueError(f"slot {slot} out of range")
+        want = (self.B, self.Sl, self.H, 128) if to_head else (self.B, self.Hl, self.S, 128)
+        if tuple(x.shape) != want or x.dtype != torch.bfloat16 or not x.is_cuda or not x.is_contiguous():
+            raise ValueError(f"expected a contiguous CUDA bf16 tensor of shape {want}")
+        i = slot if to_head else self.slots + slot
+        T, Hh, W = self.grid
+        self._barrier()
+        with torch.cuda.device(self.device):
+            rc = self._lib.fba_peer_exchange(x.data_ptr(), self._peer_ptrs[i], self.world, self.rank, self.B, self.H,
+                                             T, Hh, W, self.tile[0], self.tile[1], self.tile[2], 1 if to_head else 0,
+                                             torch.cuda.current_stream(self.device).cuda_stream)
+        self._check(rc, "fba_peer_exchange")
+        self._barrier()
+        shape = (self.B, self.Hl, self.S, 128) if to_head else (self.B, self.Sl, self.H, 128)
+        return self._views[i].view(shape)
+
+    def seq_to_head(self, x: torch.Tensor, slot: int = 0) -> torch.Tensor:
+        """[B, S/P, H, 128] raster chunk -> [B, H/P, S, 128] tile-major, local heads (aliases slot)."""
+        return self._run(x, True, slot)
+
+    def head_to_seq(self, y: torch.Tensor, slot: int = 0) -> torch.Tensor:
+        """[B, H/P, S, 128] tile-major, local heads -> [B, S/P, H, 128] raster chunk (aliases slot)."""
+        return self._run(y, False, slot)
+
+    def close(self):
+        if self._closed:
+            return
+        self._closed = True
+        torch.cuda.synchronize(self.device)
+        self._barrier()
+        torch.cuda.synchronize(self.device)
+        self._views = []
+        with torch.cuda.device(self.device):
+            for p in self._opened:
+                self._lib.fba_peer_close(p)
+            self._barrier()   # nobody frees while a peer still has the buffer mapped
+            torch.cuda.synchronize(self.device)
+            for p in self._own:
+                self._lib.fba_peer_free(p)
+        self._opened, self._own = [], []

@@ -200,6 +200,33 @@ int fba_bwd_static_scratch(const void* q, const void* k, const void* v, const vo
                            int Hq, int Hkv, int Sq, int Skv, const fba_list_t* k2q, uint32_t* status,
                            void* stream);
 
+/*
+ * Sequence <-> head exchange over peer memory, fused with the token reorder (no counterpart in the
+ * reference, which is single-GPU; its callers' layouts are benchmark/dynamic/random/scripts/
+ * random_fwd.py:58-60).  With the sequence of a [B, S, H, 128] raster-order (t, h, w) activation
+ * sharded over n_ranks GPUs (rank r holds rows r*S/n .. (r+1)*S/n), every GPU needs
+ * [B, H/n, S, 128] for its heads, tokens in tile-major order (tiles of tt x th x tw; 1 x 1 x 1
+ * keeps raster order).  fba_peer_exchange reads the local tensor once and stores each 256-byte
+ * row into its final place in the owning GPU's destination buffer:
+ *   to_head != 0: src [B, S/n, H, 128] raster chunk  -> peers[h / (H/n)] as [B, H/n, S, 128] tile-major
+ *   to_head == 0: src [B, H/n, S, 128] tile-major    -> peers[owner of the raster row] as [B, S/n, H, 128]
+ * peers[i] is rank i's destination buffer as addressable from THIS process (peers[rank] is the
+ * local one).  The kernel waits on nothing; the caller orders it against the other GPUs with a
+ * barrier before (destinations no longer read) and after (rows have landed).
+ *
+ * Destination buffers are plain cudaMalloc memory shared through CUDA IPC:
+ *   fba_peer_alloc / fba_peer_free   on the owning process (current device),
+ *   fba_peer_export                  64-byte handle to send to the other processes,
+ *   fba_peer_open / fba_peer_close   map / unmap another process's buffer (enables peer access).
+ */
+int fba_peer_alloc(uint64_t bytes, void** ptr);
+int fba_peer_free(void* ptr);
+int fba_peer_export(const void* ptr, unsigned char* handle64);
+int fba_peer_open(const unsigned char* handle64, void** ptr);
+int fba_peer_close(void* ptr);
+int fba_peer_exchange(const void* src, void* const* peers, int n_ranks, int rank, int B, int H, int T,
+                      int Hh, int W, int tt, int th, int tw, int to_head, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -75,3 +75,37 @@ def test_ulysses_exchange_world2():
         ret = m.dict()
         mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
         assert dict(ret) == {0: "ok", 1: "ok"}
+
+
+@pytest.mark.parametrize("world,grid,tile", [(2, (2, 4, 4), (1, 2, 2)), (4, (4, 4, 8), (2, 2, 4)), (2, (1, 1, 64), (1, 1, 1))])
+def test_peer_exchange_row_map_is_transpose_plus_tile_major(world, grid, tile):
+    """The row map of the fused peer exchange, emulated for all ranks in one process: scattering
+    every rank's [B, S/P, H] raster chunk by it gives transpose + tile-major permutation + head
+    sharding; the way back restores the chunks."""
+    from flex_block_attn_b200.dist import peer_exchange_rows
+    from flex_block_attn_b200.masks import tile_major_permutation
+
+    B, H, D = 2, 4, 3
+    S = grid[0] * grid[1] * grid[2]
+    Hl, Sl = H // world, S // world
+    x = torch.arange(B * S * H * D, dtype=torch.float32).reshape(B, S, H, D)      # global, raster order
+    want_heads = x.transpose(1, 2)[:, :, tile_major_permutation(grid, tile)]     # [B, H, S, D] tile-major
+    head_bufs = [torch.full((B * Hl * S, D), -1.0) for _ in range(world)]
+    for r in range(world):
+        chunk = x[:, r * Sl:(r + 1) * Sl].reshape(-1, D)
+        dest, row = peer_exchange_rows(r, world, B, H, grid, tile, True)
+        assert dest.numel() == chunk.shape[0]
+        for d in range(world):
+            sel = dest == d
+            head_bufs[d][row[sel]] = chunk[sel]
+    for r in range(world):
+        assert torch.equal(head_bufs[r].reshape(B, Hl, S, D), want_heads[:, r * Hl:(r + 1) * Hl])
+    seq_bufs = [torch.full((B * Sl * H, D), -1.0) for _ in range(world)]
+    for r in range(world):
+        src = head_bufs[r]
+        dest, row = peer_exchange_rows(r, world, B, H, grid, tile, False)
+        for d in range(world):
+            sel = dest == d
+            seq_bufs[d][row[sel]] = src[sel]
+    for r in range(world):
+        assert torch.equal(seq_bufs[r].reshape(B, Sl, H, D), x[:, r * Sl:(r + 1) * Sl])

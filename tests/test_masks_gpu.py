@@ -86,3 +86,40 @@ def test_tile_major_layout_change_is_exact(grid, tile):
     assert got.shape == (B, Hn, S, 128) and torch.equal(got, want)
     back = masks.from_tile_major(got, grid, tile)
     assert torch.equal(back, x)
+
+
+@pytest.mark.parametrize("world,grid,tile", [(2, (2, 8, 8), (2, 4, 4)), (4, (3, 8, 16), (3, 4, 8)), (8, (4, 8, 8), (1, 1, 1))])
+def test_peer_exchange_kernel_with_emulated_ranks(world, grid, tile):
+    """fba_peer_exchange with every "rank" on one GPU (its peer pointers are local buffers): the
+    union of all ranks' stores is transpose + tile-major reorder + head sharding, bit for bit, and
+    the way back restores every rank's raster chunk."""
+    import ctypes
+
+    from flex_block_attn_b200 import _cabi, masks
+
+    lib = _cabi.lib()
+    B, H = 2, 8
+    S = grid[0] * grid[1] * grid[2]
+    Hl, Sl = H // world, S // world
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn((B, S, H, 128), generator=g, device="cuda").to(torch.bfloat16)
+    want = masks.to_tile_major(x, grid, tile)                                   # [B, H, S, 128]
+    stream = torch.cuda.current_stream().cuda_stream
+    head_bufs = [torch.zeros((B, Hl, S, 128), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    ptrs = (ctypes.c_void_p * world)(*[t.data_ptr() for t in head_bufs])
+    chunks = [x[:, r * Sl:(r + 1) * Sl].contiguous() for r in range(world)]
+    for r in range(world):
+        rc = lib.fba_peer_exchange(chunks[r].data_ptr(), ptrs, world, r, B, H, *grid, *tile, 1, stream)
+        _cabi.check(rc, "fba_peer_exchange")
+    for r in range(world):
+        assert torch.equal(head_bufs[r], want[:, r * Hl:(r + 1) * Hl])
+    seq_bufs = [torch.zeros((B, Sl, H, 128), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    ptrs2 = (ctypes.c_void_p * world)(*[t.data_ptr() for t in seq_bufs])
+    for r in range(world):
+        rc = lib.fba_peer_exchange(head_bufs[r].data_ptr(), ptrs2, world, r, B, H, *grid, *tile, 0, stream)
+        _cabi.check(rc, "fba_peer_exchange")
+    for r in range(world):
+        assert torch.equal(seq_bufs[r], chunks[r])
+    # argument checks
+    assert lib.fba_peer_exchange(chunks[0].data_ptr(), ptrs, 3, 0, B, H, *grid, *tile, 1, stream) == -1
+    assert lib.fba_peer_exchange(chunks[0].data_ptr(), ptrs, world, world, B, H, *grid, *tile, 1, stream) == -1
