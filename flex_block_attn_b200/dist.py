@@ -291,3 +291,52 @@ class PeerExchange:
             for p in self._own:
                 self._lib.fba_peer_free(p)
         self._opened, self._own = [], []
+
+
+class _PeerSeqToHead(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, ex, slot, grad_slot):
+        ctx.ex, ctx.grad_slot = ex, grad_slot
+        return ex.seq_to_head(x.contiguous(), slot)
+
+    @staticmethod
+    def backward(ctx, g):
+        # cloned: autograd may keep the returned tensor as the leaf's .grad, and the slot is reused
+        return ctx.ex.head_to_seq(g.contiguous(), ctx.grad_slot).clone(), None, None, None
+
+
+class _PeerHeadToSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, ex, slot, grad_slot):
+        ctx.ex, ctx.grad_slot = ex, grad_slot
+        return ex.head_to_seq(x.contiguous(), slot)
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.ex.seq_to_head(g.contiguous(), ctx.grad_slot), None, None, None
+
+
+def ulysses_tile_major_attn(q, k, v, q_block_size, kv_block_size, mask_fn: Callable, exchange: PeerExchange,
+                            attn_fn: Optional[Callable] = None):
+    """Block-sparse attention for sequence-sharded activations in their native layout.
+
+    q, k, v: [B, S/P, H, 128] bf16, this rank's contiguous chunk of the raster-order (t, h, w)
+    sequence with all heads (self-attention: q and k/v have the same heads and length).  The
+    fused peer exchange delivers [B, H/P, S, 128] in the tile-major order of ``exchange``;
+    ``mask_fn(q_h, k_h)`` returns the block mask (or ``SparseLists``) for the local heads in that
+    order; the output comes back as [B, S/P, H, 128] raster order.  Differentiable: the gradients
+    take the same two kernels in the opposite direction.  ``exchange`` needs at least 4 slots
+    (q, k, v and dO travel towards the heads; O, dQ, dK, dV back) and the output aliases slot 0 of
+    its sequence-side buffers until the next call.
+    """
+    if exchange.slots < 4:
+        raise ValueError("ulysses_tile_major_attn needs a PeerExchange with at least 4 slots")
+    if attn_fn is None:
+        from .interface import flex_block_attn_func as attn_fn  # noqa: N813
+    qh = _PeerSeqToHead.apply(q, exchange, 0, 1)
+    kh = _PeerSeqToHead.apply(k, exchange, 1, 2)
+    vh = _PeerSeqToHead.apply(v, exchange, 2, 3)
+    with torch.no_grad():
+        mask = mask_fn(qh, kh)
+    oh = attn_fn(qh, kh, vh, q_block_size, kv_block_size, mask)
+    return _PeerHeadToSeq.apply(oh, exchange, 0, 3)

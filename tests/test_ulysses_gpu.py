@@ -114,6 +114,37 @@ def _peer_worker(rank, world, port, ret):
             torch.cuda.synchronize()
         finally:
             ex.close()
+
+        # attention on natively laid-out, sequence-sharded activations vs one GPU doing everything
+        import flex_block_attn_b200 as fba
+        from tests.util import assert_close
+
+        B, H, grid, tile, qb, kb = 1, 4, (2, 8, 24), (1, 8, 8), 128, 128      # S = 384: 6 tiles of 64 tokens
+        S = grid[0] * grid[1] * grid[2]
+        Sl, Hl = S // world, H // world
+        full = [torch.randn((B, S, H, 128), generator=g).to(torch.bfloat16).to(dev) for _ in range(4)]
+        sl = slice(rank * Sl, (rank + 1) * Sl)
+        ql, kl, vl = (t[:, sl].contiguous().requires_grad_() for t in full[:3])
+        n_tiles = S // 128
+        mask = torch.ones((n_tiles, n_tiles), dtype=torch.bool, device=dev).tril()
+        ex = fd.PeerExchange(B, H, grid, tile, slots=4)
+        try:
+            o = fd.ulysses_tile_major_attn(ql, kl, vl, qb, kb, lambda qh, kh: mask, ex)
+            o_keep = o.clone()
+            o.backward(full[3][:, sl].contiguous())
+            torch.cuda.synchronize()
+            fba.check_status(dev)
+            tm = lambda t: masks.to_tile_major(t.contiguous(), grid, tile)           # [B, H, S, 128]
+            rs = lambda t: masks.from_tile_major(t.contiguous(), grid, tile)         # [B, S, H, 128]
+            qf, kf, vf = (tm(t).requires_grad_() for t in full[:3])
+            of = fba.flex_block_attn_func(qf, kf, vf, qb, kb, mask)
+            of.backward(tm(full[3]))
+            torch.cuda.synchronize()
+            assert torch.equal(o_keep, rs(of.detach())[:, sl]), "forward differs from the single-GPU result"
+            assert torch.equal(kl.grad, rs(kf.grad)[:, sl]) and torch.equal(vl.grad, rs(vf.grad)[:, sl])
+            assert_close(ql.grad.float(), rs(qf.grad)[:, sl].float(), "dQ", max_abs=1e-2)
+        finally:
+            ex.close()
         ret[rank] = "ok"
     except Exception as e:  # pragma: no cover - surfaced through ret
         ret[rank] = f"{type(e).__name__}: {e}"
