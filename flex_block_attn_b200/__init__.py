@@ -11,6 +11,7 @@ from .interface import (  # noqa: F401
     check_status,
     flex_block_attn_func,
     forward_with_lists,
+    moba_lists,
     ssta_lists,
     sta_lists,
 )
@@ -28,4 +29,5 @@ __all__ = [
     "SparseLists",
     "sta_lists",
     "ssta_lists",
+    "moba_lists",
 ]

@@ -21,7 +21,7 @@
 //                           accumulator with 16-byte vector reductions (red.global.add.v4.f32).
 //   3. bwd_dq_convert_kernel  dQ fp32 accumulator (tile-blocked layout) -> bf16 [B,H,Sq,128].
 //
-// Warp roles of the main kernel (448 threads): warps 0-7 compute P^T and dS^T (thread = key row;
+// Warp roles of the main kernel (512 threads): warps 0-7 compute P^T and dS^T (thread = key row;
 // warps 0-3 take query columns 0-63 of the tile, warps 4-7 columns 64-127), warps 8-11 drain dQ
 // from TMEM, warps 12 and 14 issue the MMAs (two independent chains), warp 13 drives TMA.
 //

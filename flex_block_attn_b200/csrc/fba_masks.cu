@@ -175,7 +175,9 @@ extern "C" int fba_ssta_index(const void* q, const void* k, int B, int Hq, int H
         Sq % q_block != 0 || Skv % kv_block != 0 || topk < 0)
         return set_error(FBA_ERR_BAD_ARG, "fba_ssta_index: bad size");
     const int nQ = Sq / q_block, nK = Skv / kv_block;
-    if (Gt <= 0 || Gh <= 0 || Gw <= 0 || static_cast<long long>(Gt) * Gh * Gw != nK || wt < 0 || wh < 0 || ww < 0)
+    // a window extent of -1 selects no tile at all in that dimension: with it the mask is the
+    // top-k selection alone (MoBA)
+    if (Gt <= 0 || Gh <= 0 || Gw <= 0 || static_cast<long long>(Gt) * Gh * Gw != nK || wt < -1 || wh < -1 || ww < -1)
         return set_error(FBA_ERR_BAD_ARG, "fba_ssta_index: the tile grid must have one tile per key block");
     if (kv_block % q_block != 0 || static_cast<long long>(nQ) * q_block != static_cast<long long>(nK) * kv_block)
         return set_error(FBA_ERR_BAD_ARG,

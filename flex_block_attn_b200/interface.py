@@ -254,6 +254,14 @@ def ssta_lists(q, k, tile_grid, q_block: int, kv_block: int, topk: int = 8, wind
     return lists, mask
 
 
+def moba_lists(q, k, q_block: int, kv_block: int, topk: int, need_bwd: bool = True):
+    """MoBA mask (for every query block the ``topk`` key blocks with the largest pooled q.k score,
+    same definition as ``masks.moba_topk_mask``) built by the SSTA kernels with the window switched
+    off.  Returns ``(lists, mask)`` like ``ssta_lists``."""
+    return ssta_lists(q, k, (1, 1, k.shape[2] // kv_block), q_block, kv_block, topk=topk, window=(-1, -1, -1),
+                      need_bwd=need_bwd)
+
+
 def _check_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
     for name, t in (("q", q), ("k", k), ("v", v)):
         if not t.is_cuda:

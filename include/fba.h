@@ -117,6 +117,8 @@ int fba_build_tile_lists(const uint8_t* mask, int mask_dim, int B, int H, int nQ
  * One key block = one tile (Gt*Gh*Gw == Skv/kv_block), q_block divides kv_block.  Writes the bool
  * mask uint8 [B, Hq, nQ, nK], the query-major list (q2k_idx int32 [B*Hq*nQ, nK], q2k_cnt) and,
  * if given, the key-major list.  `scratch` holds fba_ssta_scratch_floats() floats.
+ * A window extent of -1 (wt = wh = ww = -1) switches the window off: the mask is then the top-k
+ * selection alone, i.e. a MoBA mask (use the grid 1 x 1 x nK).
  */
 int fba_sta_index(int Gt, int Gh, int Gw, int wt, int wh, int ww, int32_t* idx, int32_t* cnt,
                   void* stream);

@@ -72,6 +72,32 @@ def test_ssta_lists_match_torch_builder(B, Hq, Hkv, grid, qb, kb, topk):
     assert bool((mask.sum(-1) >= min(topk, n_tiles)).all())
 
 
+@pytest.mark.parametrize("qb,kb,topk", [(128, 384, 3), (384, 384, 5), (128, 128, 1)])
+def test_moba_lists_match_torch_builder(qb, kb, topk):
+    """Top-k selection alone (window switched off): same mask as masks.moba_topk_mask up to
+    numerical ties, exactly ``topk`` blocks per row, lists = compaction of the mask, and attention
+    over the lists matches the oracle over the mask."""
+    import flex_block_attn_b200 as fba
+    from flex_block_attn_b200 import masks
+    from tests.util import assert_close
+
+    B, Hq, Hkv, S = 1, 4, 2, 3072
+    q, k, v, do = rand_qkv(B, Hq, Hkv, S, S, seed=70 + topk, device="cuda")
+    lists, mask = fba.moba_lists(q, k, qb, kb, topk)
+    want = masks.moba_topk_mask(q, k, qb, kb, topk)
+    assert mask.shape == want.shape and bool((mask.sum(-1) == topk).all())
+    assert (mask != want).any(-1).float().mean().item() < 0.01
+    q2k_idx, q2k_cnt, k2q_idx, k2q_cnt = orc.block_index_oracle(mask.cpu())
+    assert torch.equal(lists.fwd_idx.cpu(), q2k_idx) and torch.equal(lists.fwd_cnt.cpu(), q2k_cnt)
+    assert torch.equal(lists.bwd_idx.cpu(), k2q_idx) and torch.equal(lists.bwd_cnt.cpu(), k2q_cnt)
+    q1, k1, v1 = (t.clone().requires_grad_() for t in (q, k, v))
+    o = fba.flex_block_attn_func(q1, k1, v1, qb, kb, lists)
+    o.backward(do)
+    ref = orc.attention_slab(q.float(), k.float(), v.float(), mask, qb, kb, do.float())
+    for g, w, nm in zip((o.detach(), q1.grad, k1.grad, v1.grad), (ref[0], ref[2], ref[3], ref[4]), ("O", "dQ", "dK", "dV")):
+        assert_close(g.float(), w, f"moba {nm}")
+
+
 @pytest.mark.parametrize("grid,tile", [((6, 8, 16), (6, 8, 8)), ((4, 4, 6), (2, 2, 3)), ((18, 48, 80), (6, 8, 8))])
 def test_tile_major_layout_change_is_exact(grid, tile):
     from flex_block_attn_b200 import masks
