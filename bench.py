@@ -109,7 +109,7 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        sm, mx, pw, reasons = [], [], [], set()
         try:
             for line in Path(self.path).read_text().splitlines():
                 parts = [x.strip() for x in line.split(",")]
@@ -120,6 +120,10 @@ class ClockSampler:
                     mx.append(float(parts[2]))
                 except ValueError:
                     continue
+                try:
+                    pw.append(float(parts[3]))
+                except ValueError:
+                    pass
                 for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
                     if val.lower().startswith("active"):
                         reasons.add(name)
@@ -128,7 +132,10 @@ class ClockSampler:
             pass
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no_samples"]}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        out = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        if pw:
+            out["power_w"] = statistics.median(pw)
+        return out
 
 
 def physical_gpu_index(local_rank: int) -> int:
