@@ -25,9 +25,8 @@
 // warps 0-3 take query columns 0-63 of the tile, warps 4-7 columns 64-127), warps 8-11 drain dQ
 // from TMEM, warps 12 and 14 issue the MMAs (two independent chains), warp 13 drives TMA.
 //
-// Shared memory: K, V resident (64 KiB); Q in three stages (96 KiB); two dO stages (64 KiB), each of
-// which is overwritten with dS^T of its iteration once dV and dP^T have read dO; the (lse2, delta)
-// rows of the current and next query tile (2 KiB).
+// Shared memory: K, V resident (64 KiB); Q double-buffered with its (lse2, delta) rows (64 + 2 KiB);
+// dO double-buffered (64 KiB); dS^T (32 KiB).
 #include "fba_common.cuh"
 
 namespace fba {
@@ -35,30 +34,27 @@ namespace fba {
 constexpr int kBwdThreads = 512;  // 4 warpgroups: compute, compute, dQ drain, {MMA, TMA, 2 idle}
 constexpr uint32_t kBwdSmemK = 0;
 constexpr uint32_t kBwdSmemV = 1 * kTileBytes;
-constexpr int kBwdQStages = 3;
-constexpr uint32_t kBwdSmemQ = 2 * kTileBytes;    // 3 stages
-constexpr uint32_t kBwdSmemDO = 5 * kTileBytes;   // 2 stages; stage (it & 1) holds dO(it), then dS^T(it)
-constexpr uint32_t kBwdSmemLD = 7 * kTileBytes;   // 2 stages x (128 x lse2, 128 x delta)
+constexpr uint32_t kBwdSmemQ = 2 * kTileBytes;    // 2 stages
+constexpr uint32_t kBwdSmemDO = 4 * kTileBytes;   // 2 stages
+constexpr uint32_t kBwdSmemDS = 6 * kTileBytes;
+constexpr uint32_t kBwdSmemLD = 7 * kTileBytes;     // 2 stages x 128 x (lse2, delta)
 constexpr uint32_t kBwdSmemBars = kBwdSmemLD + 2 * 1024;
 
 
 enum BwdBar : uint32_t {
     kBKvFull = 0,
-    kBQFull = 1,      // 3: Q(it) is in stage it % 3
-    kBQEmpty = 4,     // 3: dK(it) has read it
-    kBDoFull = 7,     // 2: dO(it) is in stage it & 1
-    kBDoEmpty = 9,    // 2 (count 2): dV(it) and dP^T(it) have read dO(it) -> dS^T(it) may overwrite it
-    kBStageFree = 11, // 2: dQ(it) and dK(it) have read dS^T(it) -> dO(it + 2) may be loaded
-    kBLdFull = 13,    // 2: the (lse2, delta) rows of Q(it) are in stage it & 1
-    kBLdEmpty = 15,   // 2 (count 256): the compute warps are done with them
-    kBSFull = 17,
-    kBPReady = 18,
-    kBDpFull = 19,
-    kBDsReady = 20,
-    kBDqFull = 21,
-    kBDqDrained = 22,
-    kBDkvDone = 23,
-    kBCount = 24
+    kBQFull = 1,      // 2
+    kBQEmpty = 3,     // 2
+    kBDoFull = 5,     // 2
+    kBDoEmpty = 7,    // 2
+    kBSFull = 9,
+    kBPReady = 10,
+    kBDpFull = 11,
+    kBDsReady = 12,
+    kBDqFull = 13,
+    kBDqDrained = 14,
+    kBDkvDone = 15,
+    kBCount = 16
 };
 // barriers, then the TMEM base slot and the abort flag
 constexpr uint32_t kBwdSmemBytes = kBwdSmemBars + 8 * kBCount + 16;
@@ -205,16 +201,13 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         mbar_init(bar(kBKvFull), 1);
-        for (int s = 0; s < kBwdQStages; ++s) {
+        for (int s = 0; s < 2; ++s) {
             mbar_init(bar(kBQFull + s), 1);
             mbar_init(bar(kBQEmpty + s), 1);
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(bar(kBDoFull + s), 1);
             mbar_init(bar(kBDoEmpty + s), 2);   // dV (issuer A) and dP^T (issuer B) both read dO
-            mbar_init(bar(kBStageFree + s), 1);
-            mbar_init(bar(kBLdFull + s), 1);
-            mbar_init(bar(kBLdEmpty + s), 256);
         }
         mbar_init(bar(kBSFull), 1);
         mbar_init(bar(kBPReady), 256);
@@ -240,7 +233,7 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     const uint32_t tST = tmem + 0, tDV = tmem + 128, tDP = tmem + 256, tDK = tmem + 384;
-    const uint32_t sK = base + kBwdSmemK, sV = base + kBwdSmemV;
+    const uint32_t sK = base + kBwdSmemK, sV = base + kBwdSmemV, sDS = base + kBwdSmemDS;
     auto sDO = [&](int s) { return base + kBwdSmemDO + static_cast<uint32_t>(s) * kTileBytes; };
     auto sQ = [&](int s) { return base + kBwdSmemQ + static_cast<uint32_t>(s) * kTileBytes; };
 
@@ -306,32 +299,20 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             bool ok = true;
             for (int it = 0; it < n_total && ok; ++it) {
                 if (it > 0) cur_next(cur);
-                const int st = it & 1, qs = it % kBwdQStages;
-                const uint32_t spar = (it >> 1) & 1u, qpar = (it / kBwdQStages) & 1u;
+                const int st = it & 1;
                 const int qt = cur.q0 + cur.u, bq = bq0 + cur.r;
-                // Q has one stage more than dO: its load for iteration it goes out as soon as the
-                // previous iteration's dO load has (i.e. when dK(it - 3) is long done), a whole
-                // iteration before S^T(it) needs it -- a tile load takes ~2500 clk here.
-                if (!mbar_wait(bar(kBQEmpty + qs), qpar ^ 1u, abort_flag)) {
+                if (!mbar_wait(bar(kBQEmpty + st), ((it >> 1) & 1u) ^ 1u, abort_flag)) {
                     report_timeout(p.status, 2, 13, it, 100);
                     ok = false;
                     break;
                 }
                 if (it < 64) FBA_TRACE_REC(p.status, 2048 + it * 4 + 0);
-                mbar_expect_tx(bar(kBQFull + qs), kTileBytes);
-                tma_load_3d(sQ(qs), &tm_q, 0, qt * 128, bq, bar(kBQFull + qs));
-                tma_load_3d(sQ(qs) + kPanelBytes, &tm_q, 64, qt * 128, bq, bar(kBQFull + qs));
-                if (!mbar_wait(bar(kBLdEmpty + st), spar ^ 1u, abort_flag)) {
-                    report_timeout(p.status, 2, 13, it, 102);
-                    ok = false;
-                    break;
-                }
-                mbar_expect_tx(bar(kBLdFull + st), 1024);
+                mbar_expect_tx(bar(kBQFull + st), kTileBytes + 1024);
+                tma_load_3d(sQ(st), &tm_q, 0, qt * 128, bq, bar(kBQFull + st));
+                tma_load_3d(sQ(st) + kPanelBytes, &tm_q, 64, qt * 128, bq, bar(kBQFull + st));
                 bulk_load(base + kBwdSmemLD + st * 1024u,
-                          p.ld + (static_cast<long long>(bq) * p.n_mtiles + qt) * 128, 1024, bar(kBLdFull + st));
-                // The dO stage doubles as the dS^T buffer of its iteration: it is free again when
-                // dQ(it - 2) and dK(it - 2) have consumed dS^T(it - 2).
-                if (!mbar_wait(bar(kBStageFree + st), spar ^ 1u, abort_flag)) {
+                          p.ld + (static_cast<long long>(bq) * p.n_mtiles + qt) * 128, 1024, bar(kBQFull + st));
+                if (!mbar_wait(bar(kBDoEmpty + st), ((it >> 1) & 1u) ^ 1u, abort_flag)) {
                     report_timeout(p.status, 2, 13, it, 101);
                     ok = false;
                     break;
@@ -368,7 +349,7 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             for (int it = 0; it < n_total && ok; ++it) {
                 const int st = it & 1;
                 if (it < 64) FBA_TRACE_REC(p.status, 1024 + it * 8 + 0);
-                wait(kBDoFull + st, (it >> 1) & 1u, it, 215);
+                wait(kBDoFull + st, (it >> 1) & 1u, it, 215);   // dO(it) has landed (normally long before P^T)
                 wait(kBPReady, it & 1u, it, 210);
                 if (!ok) break;
                 tc_fence_after();
@@ -377,12 +358,11 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 umma_commit(bar(kBDoEmpty + st));     // one of the two releases of dO(it)
                 if (it + 1 < n_total) {
                     if (it < 64) FBA_TRACE_REC(p.status, 2048 + it * 4 + 2);
-                    const int qn = (it + 1) % kBwdQStages;
-                    wait(kBQFull + qn, ((it + 1) / kBwdQStages) & 1u, it, 211);
+                    wait(kBQFull + (st ^ 1), ((it + 1) >> 1) & 1u, it, 211);
                     if (!ok) break;
                     tc_fence_after();
                     if (it < 64) FBA_TRACE_REC(p.status, 1024 + it * 8 + 7);
-                    mma_tile_kk(tST, sK, sQ(qn), false);
+                    mma_tile_kk(tST, sK, sQ(st ^ 1), false);
                     umma_commit(bar(kBSFull));
                 }
                 if (it < 64) FBA_TRACE_REC(p.status, 1024 + it * 8 + 2);
@@ -415,11 +395,10 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 if (!ok) break;
                 tc_fence_after();
                 if (it < 64) FBA_TRACE_REC(p.status, 1024 + it * 8 + 3);
-                mma_tile_mm(tDP, sDO(st), sK, false);     // dQ first: its drain overlaps the dK GEMM
+                mma_tile_mm(tDP, sDS, sK, false);     // dQ first: its drain overlaps the dK GEMM
                 umma_commit(bar(kBDqFull));
-                mma_tile_km(tDK, sDO(st), sQ(it % kBwdQStages), it > 0);
-                umma_commit(bar(kBQEmpty + it % kBwdQStages));
-                umma_commit(bar(kBStageFree + st));
+                mma_tile_km(tDK, sDS, sQ(st), it > 0);
+                umma_commit(bar(kBQEmpty + st));
                 if (it < 64) FBA_TRACE_REC(p.status, 1024 + it * 8 + 4);
                 if (it + 1 < n_total) {
                     wait(kBDoFull + (st ^ 1), ((it + 1) >> 1) & 1u, it, 214);
@@ -507,7 +486,7 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     const float4* lse4 = reinterpret_cast<const float4*>(base_ptr + kBwdSmemLD + st * 1024) + 16 * h;
                     const float4* del4 = lse4 + 32;
                     if (!mbar_wait(bar(kBSFull), it & 1u, abort_flag) ||
-                        !mbar_wait(bar(kBLdFull + st), (it >> 1) & 1u, abort_flag)) {
+                        !mbar_wait(bar(kBQFull + st), (it >> 1) & 1u, abort_flag)) {
                         if (lane == 0) report_timeout(p.status, 2, static_cast<uint32_t>(warp), it, 400);
                         ok = false;
                     }
@@ -559,15 +538,15 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     if (!ok) break;
                     tc_fence_after();
                     if (warp == 0 && lane == 0 && it < 64) FBA_TRACE_REC(p.status, it * 8 + 2);
-                    uint8_t* ds_row = base_ptr + kBwdSmemDO + static_cast<uint32_t>(st) * kTileBytes +
-                                      static_cast<uint32_t>(h) * kPanelBytes + static_cast<uint32_t>(row) * 128u;
+                    uint8_t* ds_row = base_ptr + kBwdSmemDS + static_cast<uint32_t>(h) * kPanelBytes +
+                                      static_cast<uint32_t>(row) * 128u;
                     uint32_t dp[64];
                     tmem_ld32(tDP + lane_base + 64u * h, reinterpret_cast<uint32_t(&)[32]>(dp[0]));
                     tmem_ld32(tDP + lane_base + 64u * h + 32u, reinterpret_cast<uint32_t(&)[32]>(dp[32]));
                     tmem_wait_ld();
-                    uint32_t wds[32];
 #pragma unroll
                     for (int q8 = 0; q8 < 8; ++q8) {
+                        uint32_t wds[4];
 #pragma unroll
                         for (int j = 0; j < 2; ++j) {
                             const int col = 8 * q8 + 4 * j;
@@ -578,26 +557,15 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                                                    sc2, make_float2(d4.z, d4.w));
                             const float2 e0 = mul2(make_float2(pr[col], pr[col + 1]), t0);
                             const float2 e1 = mul2(make_float2(pr[col + 2], pr[col + 3]), t1);
-                            wds[4 * q8 + 2 * j] = pack_bf16x2(e0.x, e0.y);
-                            wds[4 * q8 + 2 * j + 1] = pack_bf16x2(e1.x, e1.y);
+                            wds[2 * j] = pack_bf16x2(e0.x, e0.y);
+                            wds[2 * j + 1] = pack_bf16x2(e1.x, e1.y);
                         }
-                    }
-                    // dS^T(it) goes where dO(it) was: wait until dV(it) and dP^T(it) have read it
-                    // (dP^T has, its result was just used; dV was issued when P^T became ready).
-                    if (!mbar_wait(bar(kBDoEmpty + st), (it >> 1) & 1u, abort_flag)) {
-                        if (lane == 0) report_timeout(p.status, 2, static_cast<uint32_t>(warp), it, 402);
-                        ok = false;
-                    }
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) break;
-#pragma unroll
-                    for (int q8 = 0; q8 < 8; ++q8)
                         *reinterpret_cast<uint4*>(ds_row + (static_cast<uint32_t>(q8 ^ (row & 7)) << 4)) =
-                            make_uint4(wds[4 * q8], wds[4 * q8 + 1], wds[4 * q8 + 2], wds[4 * q8 + 3]);
+                            make_uint4(wds[0], wds[1], wds[2], wds[3]);
+                    }
                     fence_proxy_async_smem();
                     tc_fence_before();
                     mbar_arrive(bar(kBDsReady));
-                    mbar_arrive(bar(kBLdEmpty + st));
                     if (warp == 0 && lane == 0 && it < 64) FBA_TRACE_REC(p.status, it * 8 + 3);
                 }
             }
