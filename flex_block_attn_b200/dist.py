@@ -276,6 +276,8 @@ class PeerExchange:
         return self._run(y, False, slot)
 
     def close(self):
+        """Unmap the peers' buffers and free the local ones (collective; idempotent).  Tensors
+        returned earlier must no longer be used."""
         if self._closed:
             return
         self._closed = True

@@ -48,6 +48,15 @@ def test_bad_arguments_return_status_codes(lib):
     assert lib.fba_fwd(None, None, None, None, None, 1, 1, 1, 128, 128, None, None, None) == -1
     assert lib.fba_set_timing_events(3, None, None) == -1
     assert lib.fba_set_timing_events(0, None, None) == 0
+    # entry points added beside the reference's interface: argument checks come before any CUDA call
+    assert lib.fba_fwd_scaled(None, None, None, None, None, 1, 1, 1, 128, 128, None, 0.1, None, None) == -1
+    assert lib.fba_bwd_scaled(*([None] * 9), 1, 1, 1, 128, 128, None, 0.1, None, None, None, None) == -1
+    p = ctypes.c_void_p()
+    assert lib.fba_peer_alloc(0, ctypes.byref(p)) == -1 and p.value is None
+    assert lib.fba_peer_export(None, None) == -1 and lib.fba_peer_open(None, ctypes.byref(p)) == -1
+    assert lib.fba_peer_free(None) == 0 and lib.fba_peer_close(None) == 0
+    assert lib.fba_peer_exchange(None, None, 2, 0, 1, 2, 1, 1, 8, 1, 1, 1, 1, None) == -1
+    assert b"fba_peer_exchange" in lib.fba_last_error()
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
