@@ -198,61 +198,3 @@ extern "C" int fba_ssta_index(const void* q, const void* k, int B, int Hq, int H
     if (k2q_idx) rc = fba_build_index(mask, 4, B, Hq, nQ, nK, nullptr, nullptr, k2q_idx, k2q_cnt, stream_);
     return rc;
 }
-
-// ---------------------------------------------------------------------------------------------
-// Layout change on either side of the operator: the reference's callers hold activations as
-// [B, S, H, 128] in raster (t, h, w) token order and transpose to [B, H, S, 128] before the call
-// (reference benchmark/dynamic/random/scripts/random_fwd.py:58-60); sliding-tile masks additionally
-// want tokens in tile-major order.  This kernel does both in one pass over the data (HBM-bound:
-// one 256-byte row read and written per token and head), in either direction.
-namespace fba {
-
-struct TileOrder {
-    int T, H, W, tt, th, tw;   // latent grid and tile extents
-    // raster position of tile-major position s
-    __device__ __forceinline__ int raster_of(int s) const {
-        const int per_tile = tt * th * tw;
-        const int tile = s / per_tile, in = s - tile * per_tile;
-        const int gw = W / tw, gh = H / th;
-        const int tw_i = tile % gw, th_i = (tile / gw) % gh, tt_i = tile / (gw * gh);
-        const int w_in = in % tw, h_in = (in / tw) % th, t_in = in / (tw * th);
-        return ((tt_i * tt + t_in) * H + (th_i * th + h_in)) * W + (tw_i * tw + w_in);
-    }
-};
-
-// to_tile_major: dst[b][h][s][:] = src[b][raster_of(s)][h][:];  otherwise the inverse.
-__global__ void __launch_bounds__(256) tile_major_kernel(const uint2* __restrict__ src, uint2* __restrict__ dst, int B,
-                                                        int Hn, int S, TileOrder ord, bool to_tile_major) {
-    const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;  // (b, h, s)
-    const long long total = static_cast<long long>(B) * Hn * S;
-    if (row >= total) return;
-    const int lane = threadIdx.x & 31;
-    const int s = static_cast<int>(row % S);
-    const int h = static_cast<int>((row / S) % Hn);
-    const long long b = row / (static_cast<long long>(S) * Hn);
-    const long long bhs = row * 32;                                        // [B, H, S, 128] in 8-byte units
-    const long long bsh = ((b * S + ord.raster_of(s)) * Hn + h) * 32;      // [B, S, H, 128]
-    if (to_tile_major) dst[bhs + lane] = src[bsh + lane];
-    else dst[bsh + lane] = src[bhs + lane];
-}
-
-}  // namespace fba
-
-extern "C" int fba_tile_major(const void* src, void* dst, int B, int Hn, int T, int H, int W, int tt, int th, int tw,
-                              int to_tile_major, void* stream_) {
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    if (!src || !dst || src == dst) return set_error(FBA_ERR_BAD_ARG, "fba_tile_major: bad pointer argument");
-    if (B <= 0 || Hn <= 0 || T <= 0 || H <= 0 || W <= 0 || tt <= 0 || th <= 0 || tw <= 0 || T % tt || H % th || W % tw)
-        return set_error(FBA_ERR_BAD_ARG, "fba_tile_major: the grid must be a positive multiple of the tile");
-    const long long S = static_cast<long long>(T) * H * W;
-    if (S > 0x7fffffffLL) return set_error(FBA_ERR_TOO_LARGE, "fba_tile_major: sequence too long");
-    int rc = bind_device_of(src);
-    if (rc != FBA_OK) return rc;
-    const long long rows = static_cast<long long>(B) * Hn * S;
-    const long long blocks = (rows * 32 + 255) / 256;
-    if (blocks > 0x7fffffffLL) return set_error(FBA_ERR_TOO_LARGE, "fba_tile_major: tensor too large");
-    TileOrder ord{T, H, W, tt, th, tw};
-    tile_major_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
-        static_cast<const uint2*>(src), static_cast<uint2*>(dst), B, Hn, static_cast<int>(S), ord, to_tile_major != 0);
-    return check_launch("tile_major_kernel");
-}

@@ -50,42 +50,85 @@ struct TokenGrid {
 //          row (b, h_l, s) goes to rank raster_of(s) / (S/P), buffer [B, S/P, H, 128].
 __global__ void __launch_bounds__(256) peer_exchange_kernel(const uint4* __restrict__ src, PeerPtrs peers, int n_ranks,
                                                            int rank, int B, int H, int S, TokenGrid grid, bool to_head) {
-    const int Hl = H / n_ranks, Sl = S / n_ranks;
-    const long long total = to_head ? static_cast<long long>(B) * Sl * H : static_cast<long long>(B) * Hl * S;
-    const int lane = threadIdx.x & 31;
-    const int half = lane >> 4, l16 = lane & 15;   // a warp moves two 256-byte rows per step, 16 bytes per lane
-    const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    const long long n_warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-    constexpr int kUnroll = 4;                      // rows in flight per half-warp
-    for (long long base = warp * (2 * kUnroll); base < total; base += n_warps * (2 * kUnroll)) {
+    // All row counts fit 32 bits (checked by the host); only byte offsets need 64.
+    const uint32_t Hl = H / n_ranks, Sl = S / n_ranks, uH = H, uS = S;
+    const uint32_t total = static_cast<uint32_t>(B) * (to_head ? Sl * uH : Hl * uS);
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t half = lane >> 4, l16 = lane & 15;   // a warp moves two 256-byte rows at a time, 16 bytes per lane
+    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const uint32_t n_warps = (gridDim.x * blockDim.x) >> 5;
+    constexpr uint32_t kUnroll = 4;                 // rows in flight per half-warp; a warp step is 8 rows
+    // The rows are enumerated so that the eight rows of a warp step form a 2 KiB contiguous run at
+    // the DESTINATION (eight consecutive tokens of one head on the way to the heads, eight
+    // consecutive heads of one token on the way back) while the eight warps of a CTA together read
+    // 16 KiB of neighbouring source rows.  That needs whole groups of eight along the walked
+    // dimension; otherwise the rows are taken in source order.
+    const bool runs = to_head ? (Sl % 8 == 0) : (Hl % 8 == 0);
+    // With tiles that are a multiple of eight tokens wide, a group of eight consecutive raster
+    // tokens starting at a multiple of eight is also consecutive in tile-major order.
+    const bool run_contig = grid.tw % 8 == 0 && (rank * Sl) % 8 == 0;
+    for (uint32_t base = warp * (2 * kUnroll); base < total; base += n_warps * (2 * kUnroll)) {
         uint4 v[kUnroll];
         uint4* dst[kUnroll];
-#pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-            const long long row = base + 2 * u + half;
-            dst[u] = nullptr;
-            if (row >= total) continue;
-            v[u] = src[row * 16 + l16];
-            int dest;
-            long long drow;
+        if (runs) {
+            const uint32_t g = base >> 3;           // base is a multiple of 8: the whole step shares g
             if (to_head) {
-                const int h = static_cast<int>(row % H);
-                const int sl = static_cast<int>((row / H) % Sl);
-                const long long b = row / (static_cast<long long>(H) * Sl);
-                dest = h / Hl;
-                drow = (b * Hl + (h - dest * Hl)) * S + grid.tile_major_of(rank * Sl + sl);
+                const uint32_t h = g % uH, t = g / uH;
+                const uint32_t s8 = t % (Sl >> 3), b = t / (Sl >> 3);
+                const uint32_t dest = h / Hl;
+                const uint32_t r0 = rank * Sl + s8 * 8;
+                const uint32_t p0 = run_contig ? grid.tile_major_of(r0) : 0u;
+                const unsigned long long srow0 = (static_cast<unsigned long long>(b) * Sl + s8 * 8) * uH + h;
+                const unsigned long long drow0 = (static_cast<unsigned long long>(b) * Hl + (h - dest * Hl)) * uS;
+#pragma unroll
+                for (uint32_t u = 0; u < kUnroll; ++u) {
+                    const uint32_t i = 2 * u + half;
+                    const uint32_t pos = run_contig ? p0 + i : static_cast<uint32_t>(grid.tile_major_of(r0 + i));
+                    v[u] = src[(srow0 + static_cast<unsigned long long>(i) * uH) * 16 + l16];
+                    dst[u] = peers.p[dest] + (drow0 + pos) * 16 + l16;
+                }
             } else {
-                const int s = static_cast<int>(row % S);
-                const int hl = static_cast<int>((row / S) % Hl);
-                const long long b = row / (static_cast<long long>(S) * Hl);
-                const int r = grid.raster_of(s);
-                dest = r / Sl;
-                drow = (b * Sl + (r - dest * Sl)) * H + rank * Hl + hl;
+                const uint32_t s_ = g % uS, t = g / uS;
+                const uint32_t hl8 = t % (Hl >> 3), b = t / (Hl >> 3);
+                const uint32_t r = grid.raster_of(s_);
+                const uint32_t dest = r / Sl;
+                const unsigned long long srow0 = (static_cast<unsigned long long>(b) * Hl + hl8 * 8) * uS + s_;
+                const unsigned long long drow0 =
+                    (static_cast<unsigned long long>(b) * Sl + (r - dest * Sl)) * uH + rank * Hl + hl8 * 8;
+#pragma unroll
+                for (uint32_t u = 0; u < kUnroll; ++u) {
+                    const uint32_t i = 2 * u + half;
+                    v[u] = src[(srow0 + static_cast<unsigned long long>(i) * uS) * 16 + l16];
+                    dst[u] = peers.p[dest] + (drow0 + i) * 16 + l16;
+                }
             }
-            dst[u] = peers.p[dest] + drow * 16 + l16;
+        } else {
+#pragma unroll
+            for (uint32_t u = 0; u < kUnroll; ++u) {
+                const uint32_t e = base + 2 * u + half;   // source row index
+                dst[u] = nullptr;
+                if (e >= total) continue;
+                uint32_t dest;
+                unsigned long long drow;
+                if (to_head) {
+                    const uint32_t h = e % uH, t = e / uH;
+                    const uint32_t sl = t % Sl, b = t / Sl;
+                    dest = h / Hl;
+                    drow = (static_cast<unsigned long long>(b) * Hl + (h - dest * Hl)) * uS +
+                           grid.tile_major_of(rank * Sl + sl);
+                } else {
+                    const uint32_t s_ = e % uS, t = e / uS;
+                    const uint32_t hl = t % Hl, b = t / Hl;
+                    const uint32_t r = grid.raster_of(s_);
+                    dest = r / Sl;
+                    drow = (static_cast<unsigned long long>(b) * Sl + (r - dest * Sl)) * uH + rank * Hl + hl;
+                }
+                v[u] = src[static_cast<unsigned long long>(e) * 16 + l16];
+                dst[u] = peers.p[dest] + drow * 16 + l16;
+            }
         }
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u)
+        for (uint32_t u = 0; u < kUnroll; ++u)
             if (dst[u] != nullptr) *dst[u] = v[u];
     }
 }
@@ -180,10 +223,25 @@ extern "C" int fba_peer_exchange(const void* src, void* const* peers, int n_rank
         return set_error(FBA_ERR_LAUNCH, "fba_peer_exchange: cannot query the device");
     }
     const long long rows = static_cast<long long>(B) * H * S / n_ranks;
+    if (rows > 0x7fffffffLL) return set_error(FBA_ERR_TOO_LARGE, "fba_peer_exchange: more than 2^31 rows per rank");
     long long blocks = (rows + 63) / 64;                       // 8 warps x 8 rows per step
     if (blocks > 8LL * sms) blocks = 8LL * sms;
     TokenGrid g{T, Hh, W, tt, th, tw};
     peer_exchange_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
         static_cast<const uint4*>(src), pp, n_ranks, rank, B, H, static_cast<int>(S), g, to_head != 0);
     return check_launch("peer_exchange_kernel");
+}
+
+// Layout change on one GPU: the reference's callers hold activations as [B, S, H, 128] in raster
+// (t, h, w) token order and transpose to [B, H, S, 128] before the call (reference
+// benchmark/dynamic/random/scripts/random_fwd.py:58-60); sliding-tile masks additionally want the
+// tokens in tile-major order.  This is the exchange above with a single rank: one HBM-bound pass,
+// one 256-byte row read and written per token and head, in either direction.
+extern "C" int fba_tile_major(const void* src, void* dst, int B, int Hn, int T, int H, int W, int tt, int th, int tw,
+                              int to_tile_major, void* stream) {
+    if (!src || !dst || src == dst) return set_error(FBA_ERR_BAD_ARG, "fba_tile_major: bad pointer argument");
+    if (B <= 0 || Hn <= 0 || T <= 0 || H <= 0 || W <= 0 || tt <= 0 || th <= 0 || tw <= 0 || T % tt || H % th || W % tw)
+        return set_error(FBA_ERR_BAD_ARG, "fba_tile_major: the grid must be a positive multiple of the tile");
+    void* peers[1] = {dst};
+    return fba_peer_exchange(src, peers, 1, 0, B, Hn, T, H, W, tt, th, tw, to_tile_major, stream);
 }

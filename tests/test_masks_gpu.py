@@ -114,8 +114,10 @@ def test_tile_major_layout_change_is_exact(grid, tile):
     assert torch.equal(back, x)
 
 
-@pytest.mark.parametrize("world,grid,tile", [(2, (2, 8, 8), (2, 4, 4)), (4, (3, 8, 16), (3, 4, 8)), (8, (4, 8, 8), (1, 1, 1))])
-def test_peer_exchange_kernel_with_emulated_ranks(world, grid, tile):
+@pytest.mark.parametrize("world,grid,tile,H", [(2, (2, 8, 8), (2, 4, 4), 8), (4, (3, 8, 16), (3, 4, 8), 8),
+                                               (8, (4, 8, 8), (1, 1, 1), 8), (2, (2, 8, 8), (1, 8, 8), 16),
+                                               (1, (2, 4, 8), (1, 2, 8), 24), (2, (1, 3, 6), (1, 1, 3), 6)])
+def test_peer_exchange_kernel_with_emulated_ranks(world, grid, tile, H):
     """fba_peer_exchange with every "rank" on one GPU (its peer pointers are local buffers): the
     union of all ranks' stores is transpose + tile-major reorder + head sharding, bit for bit, and
     the way back restores every rank's raster chunk."""
@@ -124,9 +126,9 @@ def test_peer_exchange_kernel_with_emulated_ranks(world, grid, tile):
     from flex_block_attn_b200 import _cabi, masks
 
     lib = _cabi.lib()
-    B, H = 2, 8
+    B = 2
     S = grid[0] * grid[1] * grid[2]
-    Hl, Sl = H // world, S // world
+    Hl, Sl = H // world, S // world     # covers both row enumerations of the kernel in both directions
     g = torch.Generator(device="cuda").manual_seed(3)
     x = torch.randn((B, S, H, 128), generator=g, device="cuda").to(torch.bfloat16)
     want = masks.to_tile_major(x, grid, tile)                                   # [B, H, S, 128]
@@ -147,5 +149,5 @@ def test_peer_exchange_kernel_with_emulated_ranks(world, grid, tile):
     for r in range(world):
         assert torch.equal(seq_bufs[r], chunks[r])
     # argument checks
-    assert lib.fba_peer_exchange(chunks[0].data_ptr(), ptrs, 3, 0, B, H, *grid, *tile, 1, stream) == -1
+    assert lib.fba_peer_exchange(chunks[0].data_ptr(), ptrs, 0, 0, B, H, *grid, *tile, 1, stream) == -1
     assert lib.fba_peer_exchange(chunks[0].data_ptr(), ptrs, world, world, B, H, *grid, *tile, 1, stream) == -1
