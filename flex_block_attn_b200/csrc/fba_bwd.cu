@@ -83,43 +83,59 @@ struct BwdParams {
 __global__ void __launch_bounds__(256) bwd_prep_kernel(const __nv_bfloat16* __restrict__ o,
                                                       const __nv_bfloat16* __restrict__ dout,
                                                       const float* __restrict__ lse,
-                                                      float2* __restrict__ ld, int Sq, int rows_pad,
-                                                      long long total_rows, float scale) {
-    const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    if (w >= total_rows) return;
-    const int lane = threadIdx.x & 31;
-    const long long bh = w / rows_pad;
-    const int r = static_cast<int>(w % rows_pad);
-    // Output layout, per 128-row query tile: 128 x (-lse2) followed by 128 x (-delta * scale),
-    // so the main kernel fetches four columns' worth of either quantity with one 16-byte
-    // shared-memory read and feeds it straight into packed fused multiply-adds.
-    float neg_lse2 = -INFINITY, neg_delta_s = 0.f;
-    if (r < Sq) {
-        const long long row = bh * Sq + r;
-        const uint2 a = reinterpret_cast<const uint2*>(o + row * 128)[lane];
-        const uint2 b = reinterpret_cast<const uint2*>(dout + row * 128)[lane];
-        const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
-        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
-        float s = 0.f;
+                                                      float2* __restrict__ ld, uint32_t Sq, uint32_t rows_pad,
+                                                      uint32_t total_rows, float scale) {
+    // A half-warp per row (16 bytes of O and of dO per lane), two rows per half-warp in flight, a
+    // grid-stride loop over groups of four rows per warp.  Row counts fit 32 bits (host-checked):
+    // 64-bit divisions per row would cost more than the row's memory traffic.
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t half = lane >> 4, l16 = lane & 15;
+    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const uint32_t n_warps = (gridDim.x * blockDim.x) >> 5;
+    for (uint32_t base = warp * 4; base < total_rows; base += n_warps * 4) {
+        uint32_t w[2];
+        bool live[2];
+        uint4 a[2], b[2];
+        float l[2];
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const float2 x = __bfloat1622float2(a2[j]);
-            const float2 y = __bfloat1622float2(b2[j]);
-            s = fmaf(x.x, y.x, s);
-            s = fmaf(x.y, y.y, s);
+        for (int u = 0; u < 2; ++u) {
+            w[u] = base + 2 * u + half;             // padded row index (b*h, r)
+            const uint32_t bh = w[u] / rows_pad;
+            const uint32_t r = w[u] - bh * rows_pad;
+            live[u] = w[u] < total_rows && r < Sq;
+            a[u] = b[u] = make_uint4(0u, 0u, 0u, 0u);
+            l[u] = -INFINITY;
+            if (live[u]) {
+                const unsigned long long row = static_cast<unsigned long long>(bh) * Sq + r;
+                a[u] = reinterpret_cast<const uint4*>(o + row * 128)[l16];
+                b[u] = reinterpret_cast<const uint4*>(dout + row * 128)[l16];
+                l[u] = lse[row];
+            }
         }
 #pragma unroll
-        for (int m = 16; m > 0; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
-        const float l = lse[row];
-        // A row that attended to nothing has LSE = -inf; -inf here makes every P of it exactly 0
-        // (exp2(s * c - inf)), and so its dS.
-        neg_lse2 = l == -INFINITY ? -INFINITY : -l * kLog2e;
-        neg_delta_s = -s * scale;
-    }
-    if (lane == 0) {
-        float* out = reinterpret_cast<float*>(ld) + (w >> 7) * 256 + (w & 127);
-        out[0] = neg_lse2;
-        out[128] = neg_delta_s;
+        for (int u = 0; u < 2; ++u) {
+            const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a[u]);
+            const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b[u]);
+            float s = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 x = __bfloat1622float2(a2[j]);
+                const float2 y = __bfloat1622float2(b2[j]);
+                s = fmaf(x.x, y.x, s);
+                s = fmaf(x.y, y.y, s);
+            }
+#pragma unroll
+            for (int m = 8; m > 0; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);   // within the half-warp
+            // Output layout, per 128-row query tile: 128 x (-lse2) followed by 128 x (-delta * scale),
+            // so the main kernel fetches four columns' worth of either quantity with one 16-byte
+            // shared-memory read.  A row that attended to nothing (LSE = -inf) and the padding rows of
+            // the last tile get -inf: every P of such a row is exp2(s * c - inf) = 0, and so is its dS.
+            if (l16 == 0 && w[u] < total_rows) {
+                float* out = reinterpret_cast<float*>(ld) + static_cast<unsigned long long>(w[u] >> 7) * 256 + (w[u] & 127);
+                out[0] = (!live[u] || l[u] == -INFINITY) ? -INFINITY : -l[u] * kLog2e;
+                out[128] = live[u] ? -s * scale : 0.f;
+            }
+        }
     }
 }
 
@@ -681,10 +697,13 @@ extern "C" int fba_bwd_scaled(const void* q, const void* k, const void* v, const
     const int rows_pad = n_mtiles * 128;
     const long long total_rows = n_bhq * rows_pad;
     {
-        const long long blocks = (total_rows * 32 + 255) / 256;
+        if (total_rows > 0x7fffff00LL) return set_error(FBA_ERR_TOO_LARGE, "fba_bwd: more than 2^31 query rows");
+        long long blocks = (total_rows + 31) / 32;             // 8 warps x 4 rows per step
+        if (blocks > 148 * 16) blocks = 148 * 16;
         bwd_prep_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
             static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dout), lse,
-            reinterpret_cast<float2*>(lse_delta), Sq, rows_pad, total_rows, softmax_scale);
+            reinterpret_cast<float2*>(lse_delta), static_cast<uint32_t>(Sq), static_cast<uint32_t>(rows_pad),
+            static_cast<uint32_t>(total_rows), softmax_scale);
         if ((rc = check_launch("bwd_prep_kernel")) != FBA_OK) return rc;
     }
     if (cudaMemsetAsync(dq_accum, 0, static_cast<size_t>(total_rows) * 128 * sizeof(float), stream) != cudaSuccess) {

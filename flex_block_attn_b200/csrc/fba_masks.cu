@@ -34,16 +34,37 @@ __global__ void sta_lists_kernel(int Gt, int Gh, int Gw, int wt, int wh, int ww,
 
 // ---------------------------------------------------------------------------------------------
 // Mean over each block of `block` consecutive rows of a bf16 [n_bh, S, 128] tensor -> fp32
-// [n_bh, S / block, 128].  One CTA of 128 threads per (bh, block); thread d owns column d and adds
-// the rows in order (a fixed order, so results do not depend on scheduling).
+// [n_bh, S / block, 128].  One CTA of 128 threads per (bh, block): thread t reads 16 bytes (columns
+// 8 (t % 16) ..) of rows t / 16, t / 16 + 8, ... and the eight row groups are then added in a fixed
+// order, so results do not depend on scheduling.  HBM-bound: one pass over the tensor.
 __global__ void __launch_bounds__(128) block_mean_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out,
                                                         int S, int block) {
+    __shared__ float part[8][128];
     const long long bh = blockIdx.y;
     const int blk = blockIdx.x;
+    const int c8 = threadIdx.x & 15, rg = threadIdx.x >> 4;
+    const uint4* src = reinterpret_cast<const uint4*>(x + (bh * S + static_cast<long long>(blk) * block) * 128) + c8;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll 4
+    for (int r = rg; r < block; r += 8) {
+        const uint4 v = src[static_cast<long long>(r) * 16];
+        const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(v2[j]);
+            acc[2 * j] += f.x;
+            acc[2 * j + 1] += f.y;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) part[rg][8 * c8 + j] = acc[j];
+    __syncthreads();
     const int d = threadIdx.x;
-    const __nv_bfloat16* src = x + (bh * S + static_cast<long long>(blk) * block) * 128 + d;
     float s = 0.f;
-    for (int r = 0; r < block; ++r) s += __bfloat162float(src[static_cast<long long>(r) * 128]);
+#pragma unroll
+    for (int g = 0; g < 8; ++g) s += part[g][d];
     out[(bh * (S / block) + blk) * 128 + d] = s / static_cast<float>(block);
 }
 
