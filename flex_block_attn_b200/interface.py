@@ -384,6 +384,7 @@ def _flex_block_attn_backward(q, k, v, o, lse, do, q_block_size, kv_block_size, 
 class FlexBlockAttnFunc(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, q_block_size, kv_block_size, block_mask, is_grad_enabled, softmax_scale=None):
+        _scale_of(softmax_scale)   # reject a bad scale before anything else
         assert q_block_size % 16 == 0, f"q_block_size ({q_block_size}) must be divisible by 16"
         assert kv_block_size % 64 == 0, f"kv_block_size ({kv_block_size}) must be divisible by 64"
         assert kv_block_size % q_block_size == 0 or q_block_size % kv_block_size == 0, \
@@ -399,6 +400,9 @@ class FlexBlockAttnFunc(torch.autograd.Function):
             # lists built ahead of time (sta_lists / ssta_lists / build_lists) instead of a bool mask
             assert (prebuilt.q_block, prebuilt.kv_block) == (q_block_size, kv_block_size), \
                 "the lists were built for other block sizes"
+            assert prebuilt.mask_dim == 2 or (prebuilt.B, prebuilt.H) == (q.shape[0], q.shape[1]), \
+                "per-(batch, head) lists must have the batch and head sizes of q"
+            assert prebuilt.fwd_idx.device == q.device, "the lists live on another device than q"
             q_block_num, kv_block_num = prebuilt.nQ, prebuilt.nK
         elif block_mask.dim() == 2:
             q_block_num, kv_block_num = block_mask.shape

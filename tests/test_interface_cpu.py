@@ -57,3 +57,18 @@ def test_mask_builders_on_cpu():
     assert ms.shape == (1, 2, 6, 2) and bool(ms[0, 0, 0, 0]) and bool(ms[0, 0, 5, 1])
     bm = masks.bernoulli_mask(1, 2, 6, 3, 0.0, 0, device="cpu")
     assert int(bm.sum()) == 12  # only the forced (scaled) diagonal
+
+
+def test_prebuilt_lists_are_checked_against_the_call():
+    """A SparseLists passed instead of a mask must fit the block sizes, (batch, head) and device."""
+    q, k, v = _qkv(S=256, H=2)
+    z = torch.zeros((4, 2), dtype=torch.int32)
+    c = torch.zeros((4,), dtype=torch.int32)
+    lists = fba.SparseLists(True, 4, 1, 3, 2, 2, 128, 128, 256, 256, z, c, None, z, c, None)   # built for 3 heads
+    with pytest.raises(AssertionError, match="batch and head sizes of q"):
+        fba.flex_block_attn_func(q, k, v, 128, 128, lists)
+    with pytest.raises(AssertionError, match="other block sizes"):
+        fba.flex_block_attn_func(q, k, v, 256, 256, lists)
+    with pytest.raises(ValueError, match="softmax_scale"):
+        lists2 = fba.SparseLists(True, 2, 1, 2, 2, 2, 128, 128, 256, 256, z, c, None, z, c, None)
+        fba.flex_block_attn_func(q, k, v, 128, 128, lists2, softmax_scale=float("nan"))
