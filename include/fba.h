@@ -21,7 +21,13 @@
  *                    (-inf for a row that attends to nothing; its output row is 0)
  *   block mask     : uint8 (bool) [nQ, nK] (mask_dim 2, shared by every batch and head) or
  *                    [B, Hq, nQ, nK] (mask_dim 4); non-zero = attend
- * The softmax scale is fixed at 1/sqrt(128) (reference .cu:177) and head_dim at 128 (.cu:833).
+ * The softmax scale is 1/sqrt(128) (the reference's constant, .cu:177) unless an entry point takes one
+ * explicitly; head_dim is fixed at 128 (.cu:833).
+ *
+ * Devices: every entry point that takes tensor pointers makes the device that owns them current on the
+ * calling thread (cudaSetDevice) and leaves it current; callers juggling several devices restore their
+ * own choice afterwards.  Host threads may call concurrently; fba_last_error() and the timing hook are
+ * per thread.
  *
  * List format ("list" = fba_list_t): for list row r, entries idx[r * stride + e], e < cnt[r], are
  * ascending; unused slots hold -1.  `rows_per_bh` is the number of list rows of one (batch, head);
