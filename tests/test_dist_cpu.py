@@ -60,6 +60,37 @@ def _worker(rank, world, port, ret):
         assert torch.allclose(ql.grad, qf.grad[:, :, sl], atol=1e-5)
         assert torch.allclose(kl.grad, kf.grad[:, :, sl], atol=1e-5)
         assert torch.allclose(vl.grad, vf.grad[:, :, sl], atol=1e-5)
+
+        # the autograd wiring of the native-layout path ([B, S/P, H, D] raster in and out), with a
+        # stand-in for PeerExchange that does the same re-layout over gloo
+        from flex_block_attn_b200.masks import tile_major_permutation
+
+        grid, tile = (2, 4, 24), (1, 4, 8)                 # S = 192, tiles of 32 tokens
+        perm = tile_major_permutation(grid, tile)
+        inv = torch.argsort(perm)
+
+        class GlooExchange:
+            slots = 4
+
+            def seq_to_head(self, x, slot=0):             # [B, S/P, H, D] raster -> [B, H/P, S, D] tile-major
+                return fd.seq_to_head(x.transpose(1, 2).contiguous())[:, :, perm].contiguous()
+
+            def head_to_seq(self, y, slot=0):
+                return fd.head_to_seq(y[:, :, inv].contiguous()).transpose(1, 2).contiguous()
+
+        raster = [t.transpose(1, 2).contiguous() for t in full]             # [B, S, H, D]
+        rl = [t[:, sl].clone() for t in raster]
+        q2, k2, v2 = (t.clone().requires_grad_() for t in rl[:3])
+        o2 = fd.ulysses_tile_major_attn(q2, k2, v2, 32, 32, lambda qh_, kh_: mask, GlooExchange(), attn_fn=_cpu_attn)
+        o2.backward(rl[3])
+        qt, kt, vt = (t[:, :, perm].clone().requires_grad_() for t in full[:3])   # tile-major, all heads
+        ot = _cpu_attn(qt, kt, vt, 32, 32, mask)
+        ot.backward(full[3][:, :, perm])
+        back = lambda t: t[:, :, inv].transpose(1, 2)[:, sl]                 # -> this rank's raster chunk
+        assert torch.allclose(o2, back(ot.detach()), atol=1e-5)
+        assert torch.allclose(q2.grad, back(qt.grad), atol=1e-5)
+        assert torch.allclose(k2.grad, back(kt.grad), atol=1e-5)
+        assert torch.allclose(v2.grad, back(vt.grad), atol=1e-5)
         ret[rank] = "ok"
     except Exception as e:  # pragma: no cover - surfaced through ret
         ret[rank] = f"{type(e).__name__}: {e}"
