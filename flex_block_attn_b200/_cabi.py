@@ -12,6 +12,8 @@ import os
 from pathlib import Path
 
 _LIB = None
+FBA_ERR_TIMEOUT = -4
+FBA_ERR_TOO_LARGE = -5
 LIB_PATH = Path(__file__).resolve().parent / "libfba_b200.so"
 
 EXPORTED_SYMBOLS = (
@@ -19,6 +21,13 @@ EXPORTED_SYMBOLS = (
     "fba_last_error",
     "fba_launch_count",
     "fba_set_timing_events",
+    "fba_check_status",
+    "fba_selftest_wait_timeout",
+    "fba_fwd_order",
+    "fba_bwd_order",
+    "fba_attn_workspace_bytes",
+    "fba_attn_forward",
+    "fba_attn_backward",
     "fba_build_index",
     "fba_build_tile_lists",
     "fba_sta_index",
@@ -53,7 +62,12 @@ class FbaList(ctypes.Structure):
         ("bh_stride", ctypes.c_int32),
         ("rows_div", ctypes.c_int32),
         ("sub", ctypes.c_int32),
+        ("order", ctypes.c_void_p),
     ]
+
+    def __init__(self, idx=None, cnt=None, msk=None, stride=0, rows_per_bh=0, bh_stride=0, rows_div=1, sub=1,
+                 order=None):
+        super().__init__(idx, cnt, msk, stride, rows_per_bh, bh_stride, rows_div, sub, order)
 
 
 def lib() -> ctypes.CDLL:
@@ -80,6 +94,20 @@ def lib() -> ctypes.CDLL:
     L.fba_launch_count.argtypes = []
     L.fba_set_timing_events.restype = i32
     L.fba_set_timing_events.argtypes = [i32, vp, vp]
+    L.fba_check_status.restype = i32
+    L.fba_check_status.argtypes = [vp, vp]
+    L.fba_selftest_wait_timeout.restype = i32
+    L.fba_selftest_wait_timeout.argtypes = [vp, ctypes.c_int64, vp, vp]
+    L.fba_fwd_order.restype = i32
+    L.fba_fwd_order.argtypes = [ctypes.POINTER(FbaList), i32, i32, i32, vp, vp]
+    L.fba_bwd_order.restype = i32
+    L.fba_bwd_order.argtypes = [ctypes.POINTER(FbaList), i32, i32, i32, i32, vp, vp]
+    L.fba_attn_workspace_bytes.restype = i32
+    L.fba_attn_workspace_bytes.argtypes = [i32] * 9 + [ctypes.POINTER(ctypes.c_uint64)]
+    L.fba_attn_forward.restype = i32
+    L.fba_attn_forward.argtypes = [vp] * 5 + [i32] * 7 + [vp, vp, i32, i32, vp, ctypes.c_uint64, vp, vp]
+    L.fba_attn_backward.restype = i32
+    L.fba_attn_backward.argtypes = [vp] * 9 + [i32] * 7 + [vp, vp, i32, i32, vp, ctypes.c_uint64, vp, vp]
     L.fba_build_index.restype = i32
     L.fba_build_index.argtypes = [vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp]
     L.fba_build_tile_lists.restype = i32
@@ -119,7 +147,7 @@ def lib() -> ctypes.CDLL:
     L.fba_peer_close.argtypes = [vp]
     L.fba_peer_exchange.restype = i32
     L.fba_peer_exchange.argtypes = [vp, ctypes.POINTER(vp)] + [i32] * 11 + [vp]
-    if L.fba_abi_version() != 1:
+    if L.fba_abi_version() != 2:
         raise RuntimeError("libfba_b200.so has an unexpected ABI version")
     _LIB = L
     return L

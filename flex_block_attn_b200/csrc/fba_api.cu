@@ -2,6 +2,8 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "fba_internal.cuh"
 
 namespace fba {
@@ -33,12 +35,38 @@ int check_launch(const char* what) {
     return FBA_ERR_LAUNCH;
 }
 
-int bind_device_of(const void* ptr) {
+// Driver entry points are resolved through the runtime so the library has no link-time dependency
+// on libcuda (it is built on machines without a driver).
+static void* driver_entry(const char* name) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !p) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return p;
+}
+
+typedef CUresult (*CtxGetFn)(CUcontext*);
+typedef CUresult (*CtxSetFn)(CUcontext);
+static CtxGetFn ctx_get_fn() {
+    static CtxGetFn fn = reinterpret_cast<CtxGetFn>(driver_entry("cuCtxGetCurrent"));
+    return fn;
+}
+static CtxSetFn ctx_set_fn() {
+    static CtxSetFn fn = reinterpret_cast<CtxSetFn>(driver_entry("cuCtxSetCurrent"));
+    return fn;
+}
+
+int DeviceGuard::bind(const void* ptr) {
     cudaPointerAttributes a;
     if (cudaPointerGetAttributes(&a, ptr) != cudaSuccess || a.type != cudaMemoryTypeDevice) {
         cudaGetLastError();
         return set_error(FBA_ERR_BAD_ARG, "pointer is not device memory");
     }
+    CtxGetFn get = ctx_get_fn();
+    if (get && ctx_set_fn() && get(&prev_) == CUDA_SUCCESS) armed_ = true;
     if (cudaSetDevice(a.device) != cudaSuccess) {
         cudaGetLastError();
         return set_error(FBA_ERR_LAUNCH, "cudaSetDevice failed for the device that owns the buffers");
@@ -46,24 +74,38 @@ int bind_device_of(const void* ptr) {
     return FBA_OK;
 }
 
+int DeviceGuard::bind_current() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        cudaGetLastError();
+        return set_error(FBA_ERR_LAUNCH, "cudaGetDevice failed");
+    }
+    CtxGetFn get = ctx_get_fn();
+    if (get && ctx_set_fn() && get(&prev_) == CUDA_SUCCESS) armed_ = true;
+    if (cudaSetDevice(dev) != cudaSuccess) {
+        cudaGetLastError();
+        return set_error(FBA_ERR_LAUNCH, "cudaSetDevice failed");
+    }
+    return FBA_OK;
+}
+
+DeviceGuard::~DeviceGuard() {
+    if (!armed_) return;
+    CUcontext now = nullptr;
+    if (ctx_get_fn()(&now) == CUDA_SUCCESS && now != prev_) ctx_set_fn()(prev_);
+}
+
+ProfRange::ProfRange(const char* name) { nvtxRangePushA(name); }
+ProfRange::~ProfRange() { nvtxRangePop(); }
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// The driver entry point is resolved through the runtime so the library has no link-time
-// dependency on libcuda (it is built on machines without a driver).
 static EncodeTiledFn encode_fn() {
     static EncodeTiledFn fn = nullptr;
-    if (fn) return fn;
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
-    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !p) {
-        cudaGetLastError();
-        return nullptr;
-    }
-    fn = reinterpret_cast<EncodeTiledFn>(p);
+    if (!fn) fn = reinterpret_cast<EncodeTiledFn>(driver_entry("cuTensorMapEncodeTiled"));
     return fn;
 }
 
@@ -92,7 +134,7 @@ int make_tmap_bf16(CUtensorMap* out, const void* base, int seq, long long n_bh, 
 extern "C" int fba_abi_version(void) { return FBA_ABI_VERSION; }
 extern "C" uint64_t fba_launch_count(void) { return __atomic_load_n(&fba::g_launches, __ATOMIC_RELAXED); }
 extern "C" int fba_set_timing_events(int which, void* start_event, void* stop_event) {
-    if (which < 0 || which > 2) return fba::set_error(FBA_ERR_BAD_ARG, "fba_set_timing_events: which must be 0, 1 or 2");
+    if (which < 0 || which > 3) return fba::set_error(FBA_ERR_BAD_ARG, "fba_set_timing_events: which must be 0, 1, 2 or 3");
     if (which != 0 && (!start_event || !stop_event))
         return fba::set_error(FBA_ERR_BAD_ARG, "fba_set_timing_events: null event");
     fba::g_ev_which = which;
@@ -101,3 +143,29 @@ extern "C" int fba_set_timing_events(int which, void* start_event, void* stop_ev
     return FBA_OK;
 }
 extern "C" const char* fba_last_error(void) { return fba::g_err; }
+
+extern "C" int fba_check_status(uint32_t* status, void* stream_) {
+    using namespace fba;
+    if (!status) return set_error(FBA_ERR_BAD_ARG, "fba_check_status: null status buffer");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    DeviceGuard guard;
+    int rc = guard.bind(status);
+    if (rc != FBA_OK) return rc;
+    uint32_t w[StatusWords::kCount] = {0};
+    if (cudaMemcpyAsync(w, status, sizeof(w), cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+        cudaStreamSynchronize(stream) != cudaSuccess) {
+        cudaError_t e = cudaGetLastError();
+        char buf[256];
+        snprintf(buf, sizeof(buf), "fba_check_status: reading the status words failed: %s", cudaGetErrorString(e));
+        return set_error(FBA_ERR_LAUNCH, buf);
+    }
+    if (w[StatusWords::kFlag] == 0) return FBA_OK;
+    cudaMemsetAsync(status, 0, sizeof(w), stream);
+    char buf[256];
+    snprintf(buf, sizeof(buf),
+             "a device-side wait timed out (kernel=%u role=%u block=(%u,%u) iter=%u tag=%u); the outputs of that "
+             "call are undefined",
+             w[StatusWords::kKernel], w[StatusWords::kRole], w[StatusWords::kBx], w[StatusWords::kBy],
+             w[StatusWords::kIter], w[StatusWords::kTag]);
+    return set_error(FBA_ERR_TIMEOUT, buf);
+}

@@ -195,8 +195,12 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int nt = blockIdx.x;          // key tile
     const int bhk = blockIdx.y;         // b * Hkv + kv head
+    // Key tile of this CTA: the blockIdx.x-th entry of the longest-first order when one is given
+    // (CTAs are dispatched in blockIdx order, so the shortest lists of the grid run last).
+    const int nt = p.list.order
+                       ? p.list.order[static_cast<long long>(p.list.bh_stride ? bhk : 0) * gridDim.x + blockIdx.x]
+                       : static_cast<int>(blockIdx.x);
     const int hr = p.Hq / p.Hkv;
     const int bq0 = (bhk / p.Hkv) * p.Hq + (bhk % p.Hkv) * hr;  // first query head of the group
     const int sub = p.list.sub;
@@ -680,13 +684,19 @@ extern "C" int fba_bwd_scaled(const void* q, const void* k, const void* v, const
     if (static_cast<long long>(k2q->rows_per_bh) * k2q->rows_div < n_ntiles ||
         static_cast<long long>(k2q->stride) * k2q->sub < n_mtiles)
         return set_error(FBA_ERR_BAD_ARG, "fba_bwd: k2q list does not cover the sequences");
+    // An entry stands for `sub` whole query tiles and a list row for `rows_div` whole key tiles: a
+    // sequence that ends inside such a group would make the kernel touch scratch past its end.
+    if (n_mtiles % k2q->sub != 0 || n_ntiles % k2q->rows_div != 0)
+        return set_error(FBA_ERR_BAD_ARG,
+                         "fba_bwd: ceil(Sq/128) must be a multiple of k2q->sub and ceil(Skv/128) of k2q->rows_div");
     if (static_cast<long long>(B) * Hq > 65535)
         return set_error(FBA_ERR_TOO_LARGE, "fba_bwd: B * Hq exceeds 65535");
 
     const long long n_bhq = static_cast<long long>(B) * Hq, n_bhk = static_cast<long long>(B) * Hkv;
     CUtensorMap tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv;
     int rc;
-    if ((rc = bind_device_of(q)) != FBA_OK) return rc;
+    DeviceGuard guard;
+    if ((rc = guard.bind(q)) != FBA_OK) return rc;
     if ((rc = make_tmap_bf16(&tm_q, q, Sq, n_bhq, 128)) != FBA_OK) return rc;
     if ((rc = make_tmap_bf16(&tm_k, k, Skv, n_bhk, 128)) != FBA_OK) return rc;
     if ((rc = make_tmap_bf16(&tm_v, v, Skv, n_bhk, 128)) != FBA_OK) return rc;
@@ -784,7 +794,8 @@ extern "C" int fba_bwd_static_scratch(const void* q, const void* k, const void* 
         return set_error(FBA_ERR_TOO_LARGE,
                          "fba_bwd_static_scratch: B * Hq * ceil(Sq/128) * 128 exceeds the built-in scratch "
                          "capacity of 131072 rows; use fba_bwd with caller-allocated scratch");
-    int rc = bind_device_of(q);
+    DeviceGuard guard;
+    int rc = guard.bind(q);
     if (rc != FBA_OK) return rc;
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {

@@ -21,11 +21,12 @@ struct ListDev {
     const int32_t* idx;
     const int32_t* cnt;
     const uint16_t* msk;
+    const int32_t* order;   // optional work-item order (see fba_fwd_order / fba_bwd_order), or null
     int stride, rows_per_bh, bh_stride, rows_div, sub;
 };
 
 inline ListDev to_dev(const fba_list_t& l) {
-    return ListDev{l.idx, l.cnt, l.msk, l.stride, l.rows_per_bh, l.bh_stride, l.rows_div, l.sub};
+    return ListDev{l.idx, l.cnt, l.msk, l.order, l.stride, l.rows_per_bh, l.bh_stride, l.rows_div, l.sub};
 }
 
 // Optional timeline probe for tuning (compiled out unless -DFBA_TRACE): CTA (0,0) stores SM clock

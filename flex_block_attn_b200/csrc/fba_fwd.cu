@@ -94,7 +94,12 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int bh = blockIdx.y;
-    const int pair = blockIdx.x;
+    // Work item of this CTA: the blockIdx.x-th entry of the (batch, head)'s longest-first order when
+    // one is given (CTAs are dispatched in blockIdx order, so the shortest items of the grid run
+    // last and the tail of the launch stays short), else blockIdx.x itself.
+    const int pair = p.list.order
+                         ? p.list.order[static_cast<long long>(p.list.bh_stride ? bh : 0) * gridDim.x + blockIdx.x]
+                         : static_cast<int>(blockIdx.x);
     const int hr = p.Hq / p.Hkv;
     const int bhk = (bh / p.Hq) * p.Hkv + (bh % p.Hq) / hr;
 
@@ -505,12 +510,18 @@ static int fwd_impl(const void* q, const void* k, const void* v, void* o, float*
         return set_error(FBA_ERR_BAD_ARG, "fba_fwd: sequence lengths below 128 are not supported");
     int rc = check_list(q2k, "fba_fwd: malformed q2k list");
     if (rc != FBA_OK) return rc;
-    if ((rc = bind_device_of(q)) != FBA_OK) return rc;
+    DeviceGuard guard;
+    if ((rc = guard.bind(q)) != FBA_OK) return rc;
     const int n_mtiles = (Sq + 127) / 128;
     const int n_ntiles = (Skv + 127) / 128;
     if (static_cast<long long>(q2k->rows_per_bh) * q2k->rows_div < n_mtiles ||
         static_cast<long long>(q2k->stride) * q2k->sub < n_ntiles)
         return set_error(FBA_ERR_BAD_ARG, "fba_fwd: q2k list does not cover the sequences");
+    // An entry stands for `sub` whole key tiles and a list row for `rows_div` whole query tiles: a
+    // sequence that ends inside such a group would make the kernel touch tiles past its end.
+    if (n_ntiles % q2k->sub != 0 || n_mtiles % q2k->rows_div != 0)
+        return set_error(FBA_ERR_BAD_ARG,
+                         "fba_fwd: ceil(Skv/128) must be a multiple of q2k->sub and ceil(Sq/128) of q2k->rows_div");
     if (static_cast<long long>(B) * Hq > 65535)
         return set_error(FBA_ERR_TOO_LARGE, "fba_fwd: B * Hq exceeds 65535");
 

@@ -118,7 +118,8 @@ extern "C" int fba_build_index(const uint8_t* mask, int mask_dim, int B, int H, 
         return set_error(FBA_ERR_BAD_ARG, "fba_build_index: idx and cnt must be given together");
     const int n_bh = mask_dim == 4 ? B * H : 1;
     const long long bh_stride = mask_dim == 4 ? static_cast<long long>(nQ) * nK : 0;
-    int rc = bind_device_of(mask);
+    DeviceGuard guard;
+    int rc = guard.bind(mask);
     if (rc != FBA_OK) return rc;
     if (q2k_idx) {
         BlockPred<false> p{mask, bh_stride, nQ, nK};
@@ -154,7 +155,8 @@ extern "C" int fba_build_tile_lists(const uint8_t* mask, int mask_dim, int B, in
     const int n_bh = mask_dim == 4 ? B * H : 1;
     const long long bh_stride = mask_dim == 4 ? static_cast<long long>(nQ) * nK : 0;
     const int nMt = (Sq + 127) / 128, nNt = (Skv + 127) / 128;
-    int rc = bind_device_of(mask);
+    DeviceGuard guard;
+    int rc = guard.bind(mask);
     if (rc != FBA_OK) return rc;
     if (want_fwd) {
         TilePred<false> p{mask, bh_stride, nQ, nK, q_block, kv_block, Sq, Skv};
@@ -166,4 +168,83 @@ extern "C" int fba_build_tile_lists(const uint8_t* mask, int mask_dim, int B, in
         rc = launch_compact(p, n_bh, nNt, nMt, bwd_idx, bwd_cnt, bwd_msk, stream);
     }
     return rc;
+}
+
+// ------------------------------------------------------------------------------------------
+// Work-item order.
+//
+// The attention grids have one CTA per work item (forward: a pair of 128-row query tiles; backward:
+// one 128-row key tile) and list lengths differ from item to item, so the last wave of a launch
+// idles SMs while the longest items finish.  CTAs are dispatched in blockIdx order: handing the
+// items of each (batch, head) out longest first leaves the shortest for the end.  The order is the
+// stable descending argsort of the item's work (the sum of the list lengths it walks): integer,
+// deterministic, bit-identical to argsort(stable=True, descending=True).
+//
+// One CTA per order row; the keys sit in shared memory and every thread ranks its items by
+// counting the items that sort before them (n^2 / 256 comparisons per thread, n = a few hundred).
+namespace fba {
+
+constexpr int kOrderMaxItems = 12288;   // keys of one order row must fit 48 KiB of shared memory
+
+__global__ void __launch_bounds__(256) work_order_kernel(const int32_t* __restrict__ cnt, int bh_stride,
+                                                         int rows_div, int n_tiles, int tiles_per_item,
+                                                         int heads_per_item, int n_items,
+                                                         int32_t* __restrict__ order) {
+    extern __shared__ int32_t key[];
+    const int g = blockIdx.x;
+    for (int i = threadIdx.x; i < n_items; i += blockDim.x) {
+        int k = 0;
+        for (int r = 0; r < heads_per_item; ++r) {
+            const long long base = static_cast<long long>(g * heads_per_item + r) * bh_stride;
+            for (int u = 0; u < tiles_per_item; ++u) {
+                const int tile = i * tiles_per_item + u;
+                if (tile < n_tiles) k += cnt[base + tile / rows_div];
+            }
+        }
+        key[i] = k;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_items; i += blockDim.x) {
+        const int ki = key[i];
+        int rank = 0;
+        for (int j = 0; j < n_items; ++j) {
+            const int kj = key[j];
+            rank += (kj > ki || (kj == ki && j < i)) ? 1 : 0;
+        }
+        order[static_cast<long long>(g) * n_items + rank] = i;
+    }
+}
+
+static int launch_order(const fba_list_t* l, const char* who, int n_order_rows, int n_tiles, int tiles_per_item,
+                        int heads_per_item, int32_t* order, cudaStream_t stream) {
+    if (!l || !l->cnt || !order) return set_error(FBA_ERR_BAD_ARG, who);
+    if (l->rows_per_bh <= 0 || l->rows_div <= 0 || (l->bh_stride != 0 && l->bh_stride != l->rows_per_bh) ||
+        static_cast<long long>(l->rows_per_bh) * l->rows_div < n_tiles)
+        return set_error(FBA_ERR_BAD_ARG, who);
+    const int n_items = (n_tiles + tiles_per_item - 1) / tiles_per_item;
+    if (n_items > kOrderMaxItems)
+        return set_error(FBA_ERR_TOO_LARGE, "work order: more than 12288 work items per (batch, head); pass order = NULL");
+    DeviceGuard guard;
+    int rc = guard.bind(order);
+    if (rc != FBA_OK) return rc;
+    work_order_kernel<<<static_cast<unsigned>(n_order_rows), 256, n_items * sizeof(int32_t), stream>>>(
+        l->cnt, l->bh_stride, l->rows_div, n_tiles, tiles_per_item, heads_per_item, n_items, order);
+    return check_launch("work_order_kernel");
+}
+
+}  // namespace fba
+
+extern "C" int fba_fwd_order(const fba_list_t* q2k, int B, int Hq, int Sq, int32_t* order, void* stream) {
+    if (B <= 0 || Hq <= 0 || Sq <= 0) return set_error(FBA_ERR_BAD_ARG, "fba_fwd_order: non-positive size");
+    const int rows = (q2k && q2k->bh_stride) ? B * Hq : 1;
+    return launch_order(q2k, "fba_fwd_order: malformed q2k list or null order", rows, (Sq + 127) / 128, 2, 1, order,
+                        static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int fba_bwd_order(const fba_list_t* k2q, int B, int Hq, int Hkv, int Skv, int32_t* order, void* stream) {
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || Skv <= 0 || Hq % Hkv != 0)
+        return set_error(FBA_ERR_BAD_ARG, "fba_bwd_order: bad size");
+    const bool per_head = k2q && k2q->bh_stride;
+    return launch_order(k2q, "fba_bwd_order: malformed k2q list or null order", per_head ? B * Hkv : 1,
+                        (Skv + 127) / 128, 1, per_head ? Hq / Hkv : 1, order, static_cast<cudaStream_t>(stream));
 }

@@ -1,5 +1,5 @@
 // Host-side helpers shared by the translation units of libfba_b200.so: error reporting,
-// launch checking and TMA tensor-map construction.
+// launch checking, device binding and TMA tensor-map construction.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -14,13 +14,37 @@ int set_error(int code, const char* msg);
 // cudaGetLastError() after a launch; returns FBA_OK or FBA_ERR_LAUNCH (with text recorded).
 int check_launch(const char* what);
 
-// Make the device that owns `ptr` current on the calling thread.  Callers may arrive on threads
-// that never touched CUDA (e.g. an autograd worker), where no context is current yet and the
-// driver-level tensor-map encoder would fail.
-int bind_device_of(const void* ptr);
+// Makes the device that owns a buffer current for the lifetime of the guard and puts the calling
+// thread's previous CUDA context back when the guard goes out of scope, so an entry point leaves no
+// trace in the caller's device selection.  Callers may arrive on threads that never touched CUDA
+// (e.g. an autograd worker), where no context is current yet and the driver-level tensor-map
+// encoder would fail; such a thread is left without a current context again afterwards.
+class DeviceGuard {
+  public:
+    DeviceGuard() = default;
+    ~DeviceGuard();
+    DeviceGuard(const DeviceGuard&) = delete;
+    DeviceGuard& operator=(const DeviceGuard&) = delete;
+    // Switch to the device that owns `ptr` (must be device memory).  FBA_OK or an error code.
+    int bind(const void* ptr);
+    // Switch to the device that is current in the runtime (for calls that take no buffer).
+    int bind_current();
+
+  private:
+    bool armed_ = false;
+    CUcontext prev_ = nullptr;
+};
+
+// Named range on the profiler timeline (NVTX) covering one entry point; a no-op without a tool.
+class ProfRange {
+  public:
+    explicit ProfRange(const char* name);
+    ~ProfRange();
+};
 
 // Record the caller-supplied timing event (fba_set_timing_events) around main kernel `which`
-// (1 = forward, 2 = backward); no-op unless that kernel was selected on this thread.
+// (1 = forward, 2 = backward main kernel, 3 = query-major dQ kernel); no-op unless that kernel was
+// selected on this thread.
 void timing_mark(int which, bool start, cudaStream_t stream);
 
 // 3-D bf16 tensor map over a [n_bh, seq, 128] tensor viewed as (col, row, bh), box = 64 columns x
@@ -28,8 +52,8 @@ void timing_mark(int which, bool start, cudaStream_t stream);
 int make_tmap_bf16(CUtensorMap* out, const void* base, int seq, long long n_bh, int box_rows);
 
 // Status-word layout written by the attention kernels when a bounded wait gives up.
-//   [0] non-zero flag   [1] kernel id (1 fwd, 2 bwd)   [2] role id   [3] blockIdx.x
-//   [4] blockIdx.y      [5] iteration                  [6] barrier tag
+//   [0] non-zero flag   [1] kernel id (1 fwd, 2 bwd, 3 dQ, 9 self-test)   [2] role id
+//   [3] blockIdx.x      [4] blockIdx.y      [5] iteration                [6] barrier tag
 struct StatusWords {
     enum { kFlag = 0, kKernel = 1, kRole = 2, kBx = 3, kBy = 4, kIter = 5, kTag = 6, kCount = 8 };
 };

@@ -170,7 +170,8 @@ extern "C" int fba_sta_index(int Gt, int Gh, int Gw, int wt, int wh, int ww, int
         return set_error(FBA_ERR_BAD_ARG, "fba_sta_index: bad grid or window");
     const long long n = static_cast<long long>(Gt) * Gh * Gw;
     if (n > 46340) return set_error(FBA_ERR_TOO_LARGE, "fba_sta_index: more than 46340 tiles");
-    int rc = bind_device_of(idx);
+    DeviceGuard guard;
+    int rc = guard.bind(idx);
     if (rc != FBA_OK) return rc;
     sta_lists_kernel<<<static_cast<unsigned>((n + 127) / 128), 128, 0, stream>>>(Gt, Gh, Gw, wt, wh, ww, idx, cnt);
     return check_launch("sta_lists_kernel");
@@ -204,7 +205,8 @@ extern "C" int fba_ssta_index(const void* q, const void* k, int B, int Hq, int H
         return set_error(FBA_ERR_BAD_ARG,
                          "fba_ssta_index: q_block must divide kv_block and both sequences must cover the same tiles");
     if (nK > 32 * kMaxPerLane) return set_error(FBA_ERR_TOO_LARGE, "fba_ssta_index: more than 1024 key blocks");
-    int rc = bind_device_of(q);
+    DeviceGuard guard;
+    int rc = guard.bind(q);
     if (rc != FBA_OK) return rc;
     float* qp = scratch;
     float* kp = scratch + static_cast<long long>(B) * Hq * nQ * 128;

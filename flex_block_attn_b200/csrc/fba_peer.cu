@@ -214,7 +214,17 @@ extern "C" int fba_peer_exchange(const void* src, void* const* peers, int n_rank
             return set_error(FBA_ERR_BAD_ARG, "fba_peer_exchange: destinations must be 16-byte aligned");
         pp.p[i] = static_cast<uint4*>(peers[i]);
     }
-    int rc = bind_device_of(src);
+    DeviceGuard guard;
+    {
+        // The local destination must not overlap the source: rows would be read after a store of
+        // this same launch had overwritten them.  (The other ranks' buffers live in other devices'
+        // memory and cannot overlap a local source.)
+        const unsigned long long bytes = static_cast<unsigned long long>(B) * H * S / n_ranks * 256ull;
+        const uintptr_t s0 = reinterpret_cast<uintptr_t>(src), d0 = reinterpret_cast<uintptr_t>(peers[rank]);
+        if (s0 < d0 + bytes && d0 < s0 + bytes)
+            return set_error(FBA_ERR_BAD_ARG, "fba_peer_exchange: source overlaps the local destination buffer");
+    }
+    int rc = guard.bind(src);
     if (rc != FBA_OK) return rc;
     // Persistent grid: a few CTAs per SM, each warp strides over groups of rows.
     int dev = 0, sms = 0;

@@ -256,6 +256,10 @@ class PeerExchange:
         if tuple(x.shape) != want or x.dtype != torch.bfloat16 or not x.is_cuda or not x.is_contiguous():
             raise ValueError(f"expected a contiguous CUDA bf16 tensor of shape {want}")
         i = slot if to_head else self.slots + slot
+        lo, hi = self._own[i], self._own[i] + self._n_elems * 2
+        if lo < x.data_ptr() + x.numel() * 2 and x.data_ptr() < hi:
+            raise ValueError("the source tensor lies inside the destination slot of this exchange; clone it or use "
+                             "another slot")
         T, Hh, W = self.grid
         self._barrier()
         with torch.cuda.device(self.device):
@@ -297,25 +301,32 @@ class PeerExchange:
 
 class _PeerSeqToHead(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, ex, slot, grad_slot):
+    def forward(ctx, x, ex, slot, grad_slot, keep):
         ctx.ex, ctx.grad_slot = ex, grad_slot
-        return ex.seq_to_head(x.contiguous(), slot)
+        y = ex.seq_to_head(x.contiguous(), slot)
+        # `keep`: the result will be saved for a backward pass.  The slot is raw peer-written memory
+        # that the next exchange through it overwrites behind autograd's back (no version counter
+        # sees those stores), so what outlives this call must be a private copy.
+        return y.clone() if keep else y
 
     @staticmethod
     def backward(ctx, g):
         # cloned: autograd may keep the returned tensor as the leaf's .grad, and the slot is reused
-        return ctx.ex.head_to_seq(g.contiguous(), ctx.grad_slot).clone(), None, None, None
+        return ctx.ex.head_to_seq(g.contiguous(), ctx.grad_slot).clone(), None, None, None, None
 
 
 class _PeerHeadToSeq(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, ex, slot, grad_slot):
+    def forward(ctx, x, ex, slot, grad_slot, keep):
         ctx.ex, ctx.grad_slot = ex, grad_slot
-        return ex.head_to_seq(x.contiguous(), slot)
+        y = ex.head_to_seq(x.contiguous(), slot)
+        return y.clone() if keep else y
 
     @staticmethod
     def backward(ctx, g):
-        return ctx.ex.seq_to_head(g.contiguous(), ctx.grad_slot), None, None, None
+        # consumed at once by the attention backward (which copies nothing out of it after it
+        # returns), so the slot view is enough here
+        return ctx.ex.seq_to_head(g.contiguous(), ctx.grad_slot), None, None, None, None
 
 
 def ulysses_tile_major_attn(q, k, v, q_block_size, kv_block_size, mask_fn: Callable, exchange: PeerExchange,
@@ -328,17 +339,23 @@ def ulysses_tile_major_attn(q, k, v, q_block_size, kv_block_size, mask_fn: Calla
     ``mask_fn(q_h, k_h)`` returns the block mask (or ``SparseLists``) for the local heads in that
     order; the output comes back as [B, S/P, H, 128] raster order.  Differentiable: the gradients
     take the same two kernels in the opposite direction.  ``exchange`` needs at least 4 slots
-    (q, k, v and dO travel towards the heads; O, dQ, dK, dV back) and the output aliases slot 0 of
-    its sequence-side buffers until the next call.
+    (q, k, v and dO travel towards the heads; O, dQ, dK, dV back).
+
+    Lifetime of the exchanged tensors: with grad mode on, the head-major q, k, v that the attention
+    saves for its backward and the returned output are private copies, so any number of layers (or
+    micro-batches, or checkpointed recomputations) may share one ``exchange``.  Without grad mode
+    nothing is saved; the inputs of the attention and the returned output then ALIAS the exchange's
+    slots and are valid until the next call through the same ``exchange``.
     """
     if exchange.slots < 4:
         raise ValueError("ulysses_tile_major_attn needs a PeerExchange with at least 4 slots")
     if attn_fn is None:
         from .interface import flex_block_attn_func as attn_fn  # noqa: N813
-    qh = _PeerSeqToHead.apply(q, exchange, 0, 1)
-    kh = _PeerSeqToHead.apply(k, exchange, 1, 2)
-    vh = _PeerSeqToHead.apply(v, exchange, 2, 3)
+    keep = torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v))
+    qh = _PeerSeqToHead.apply(q, exchange, 0, 1, keep)
+    kh = _PeerSeqToHead.apply(k, exchange, 1, 2, keep)
+    vh = _PeerSeqToHead.apply(v, exchange, 2, 3, keep)
     with torch.no_grad():
         mask = mask_fn(qh, kh)
     oh = attn_fn(qh, kh, vh, q_block_size, kv_block_size, mask)
-    return _PeerHeadToSeq.apply(oh, exchange, 0, 3)
+    return _PeerHeadToSeq.apply(oh, exchange, 0, 3, keep)

@@ -32,35 +32,89 @@ from ._cabi import FbaList
 HEAD_DIM = 128
 TILE = 128
 
-_status_bufs: dict[int, torch.Tensor] = {}
+class _StatusMonitor:
+    """Per-device status words (written by a kernel whose bounded wait gave up) and a pinned host
+    mirror that is refreshed asynchronously after every call, so that a timeout is noticed at the
+    next call without any synchronisation."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.buf = torch.zeros(8, dtype=torch.int32, device=device)
+        self.host = torch.zeros(8, dtype=torch.int32).pin_memory()
+        self.event = torch.cuda.Event()
+        self.pending = False
+
+    def after_call(self) -> None:
+        self.host.copy_(self.buf, non_blocking=True)
+        self.event.record(torch.cuda.current_stream(self.device))
+        self.pending = True
+
+    def poll(self) -> None:
+        """Raise if a mirror copy that has already completed shows a timed-out wait."""
+        if self.pending and self.event.query():
+            self.pending = False
+            if int(self.host[0]) != 0:
+                self.raise_from(self.host.tolist())
+
+    def raise_from(self, words) -> None:
+        self.buf.zero_()
+        self.host.zero_()
+        raise RuntimeError(
+            "flex_block_attn_b200: a device-side wait timed out; the outputs of that call are undefined "
+            f"(kernel={words[1]} role={words[2]} block=({words[3]},{words[4]}) iter={words[5]} tag={words[6]})"
+        )
+
+
+_monitors: dict[int, _StatusMonitor] = {}
+
+
+def _monitor(device: torch.device) -> _StatusMonitor:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    mon = _monitors.get(key)
+    if mon is None:
+        mon = _StatusMonitor(torch.device("cuda", key))
+        _monitors[key] = mon
+    return mon
 
 
 def _status(device: torch.device) -> torch.Tensor:
     """Per-device 8-word status buffer the kernels write when a bounded wait gives up."""
-    key = device.index if device.index is not None else torch.cuda.current_device()
-    buf = _status_bufs.get(key)
-    if buf is None:
-        buf = torch.zeros(8, dtype=torch.int32, device=device)
-        _status_bufs[key] = buf
-    return buf
+    return _monitor(device).buf
 
 
 def check_status(device: Optional[torch.device] = None) -> None:
-    """Synchronise and raise if any kernel on ``device`` reported a timed-out wait."""
+    """Synchronise the current stream of ``device`` and raise if any kernel reported a timed-out
+    wait.  Every call of this package also polls, without synchronising, a host mirror of the status
+    words refreshed after the previous calls; a training loop that wants the check to be exact calls
+    this once per step, where it synchronises anyway."""
     if device is None:
         device = torch.device("cuda", torch.cuda.current_device())
-    words = _status(device).cpu().tolist()
-    if words[0] != 0:
-        _status(device).zero_()
-        raise RuntimeError(
-            "flex_block_attn_b200: a device-side wait timed out "
-            f"(kernel={words[1]} role={words[2]} block=({words[3]},{words[4]}) iter={words[5]} tag={words[6]})"
-        )
+    mon = _monitor(device)
+    rc = _cabi.lib().fba_check_status(mon.buf.data_ptr(), _stream_ptr(device))
+    mon.pending = False
+    if rc == _cabi.FBA_ERR_TIMEOUT:
+        mon.host.zero_()
+        raise RuntimeError("flex_block_attn_b200: " + _cabi.lib().fba_last_error().decode("utf-8", "replace"))
+    _cabi.check(rc, "fba_check_status")
 
 
 def _maybe_check(device: torch.device) -> None:
     if os.environ.get("FBA_CHECK_STATUS", "0") == "1":
         check_status(device)
+    else:
+        _monitor(device).after_call()
+
+
+def _new(shape_or_like, dtype=None, device=None) -> torch.Tensor:
+    """Output / scratch allocation: uninitialised, or NaN-filled under FBA_POISON_OUTPUTS=1 (the test
+    suite sets it so that an element no kernel wrote shows up in every comparison)."""
+    if isinstance(shape_or_like, torch.Tensor):
+        t = torch.empty_like(shape_or_like)
+    else:
+        t = torch.empty(shape_or_like, dtype=dtype, device=device)
+    if os.environ.get("FBA_POISON_OUTPUTS", "0") == "1" and t.is_floating_point():
+        t.fill_(float("nan"))
+    return t
 
 
 def _stream_ptr(device: torch.device) -> int:
@@ -96,27 +150,68 @@ class SparseLists:
     bwd_idx: Optional[torch.Tensor]
     bwd_cnt: Optional[torch.Tensor]
     bwd_msk: Optional[torch.Tensor]
+    # work-item orders (longest list first), built on first use; the backward one depends on the
+    # number of kv heads (a CTA walks the lists of a whole grouped-query group)
+    fwd_order: Optional[torch.Tensor] = None
+    bwd_order: Optional[dict] = None
 
-    def fwd_list(self) -> FbaList:
+    def fwd_list(self, ordered: bool = False) -> FbaList:
         n_mt = (self.Sq + TILE - 1) // TILE
         rows = self.nQ if self.aligned else n_mt
-        return FbaList(
+        lst = FbaList(
             self.fwd_idx.data_ptr(), self.fwd_cnt.data_ptr(), _ptr(self.fwd_msk),
             self.fwd_idx.shape[-1], rows, rows if self.mask_dim == 4 else 0,
             self.q_block // TILE if self.aligned else 1,
             self.kv_block // TILE if self.aligned else 1,
         )
+        if ordered and _work_order_enabled():
+            if self.fwd_order is None:
+                dev = self.fwd_idx.device
+                n_rows = self.B * self.H if self.mask_dim == 4 else 1
+                order = torch.empty((n_rows, (n_mt + 1) // 2), dtype=torch.int32, device=dev)
+                with torch.cuda.device(dev):
+                    rc = _cabi.lib().fba_fwd_order(ctypes.byref(lst), self.B, self.H, self.Sq, order.data_ptr(),
+                                                   _stream_ptr(dev))
+                if rc != _cabi.FBA_ERR_TOO_LARGE:
+                    _cabi.check(rc, "fba_fwd_order")
+                    self.fwd_order = order
+            lst.order = _ptr(self.fwd_order)
+        return lst
 
-    def bwd_list(self) -> FbaList:
+    def bwd_list(self, Hq: Optional[int] = None, Hkv: Optional[int] = None) -> FbaList:
+        """``Hq`` / ``Hkv`` given: also attach the longest-first work order for that head grouping."""
         assert self.bwd_idx is not None and self.bwd_cnt is not None
         n_nt = (self.Skv + TILE - 1) // TILE
         rows = self.nK if self.aligned else n_nt
-        return FbaList(
+        lst = FbaList(
             self.bwd_idx.data_ptr(), self.bwd_cnt.data_ptr(), _ptr(self.bwd_msk),
             self.bwd_idx.shape[-1], rows, rows if self.mask_dim == 4 else 0,
             self.kv_block // TILE if self.aligned else 1,
             self.q_block // TILE if self.aligned else 1,
         )
+        if Hq is not None and Hkv is not None and _work_order_enabled():
+            if self.bwd_order is None:
+                self.bwd_order = {}
+            B = self.B if self.mask_dim == 4 else 1
+            if (Hq, Hkv) not in self.bwd_order:
+                dev = self.bwd_idx.device
+                n_rows = B * Hkv if self.mask_dim == 4 else 1
+                order = torch.empty((n_rows, n_nt), dtype=torch.int32, device=dev)
+                with torch.cuda.device(dev):
+                    rc = _cabi.lib().fba_bwd_order(ctypes.byref(lst), B, Hq, Hkv, self.Skv, order.data_ptr(),
+                                                   _stream_ptr(dev))
+                if rc == _cabi.FBA_ERR_TOO_LARGE:
+                    order = None
+                else:
+                    _cabi.check(rc, "fba_bwd_order")
+                self.bwd_order[(Hq, Hkv)] = order
+            lst.order = _ptr(self.bwd_order[(Hq, Hkv)])
+        return lst
+
+
+def _work_order_enabled() -> bool:
+    """FBA_WORK_ORDER=0 launches the attention grids in natural tile order (for A/B timing)."""
+    return os.environ.get("FBA_WORK_ORDER", "1") != "0"
 
 
 def build_index(block_mask: torch.Tensor, want_q2k: bool = True, want_k2q: bool = True):
@@ -303,9 +398,10 @@ def forward_with_lists(q, k, v, lists: SparseLists, softmax_scale=None, need_lse
     B, Hq, Sq, _ = q.shape
     Hkv, Skv = k.shape[1], k.shape[2]
     dev = q.device
-    o = torch.empty_like(q)
-    lse = torch.empty((B, Hq, Sq), dtype=torch.float32, device=dev) if need_lse else None
-    lst = lists.fwd_list()
+    o = _new(q)
+    lse = _new((B, Hq, Sq), torch.float32, dev) if need_lse else None
+    _monitor(dev).poll()
+    lst = lists.fwd_list(ordered=True)
     with torch.cuda.device(dev):
         rc = _cabi.lib().fba_fwd_scaled(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
                                         lse.data_ptr() if need_lse else None, B, Hq, Hkv, Sq, Skv,
@@ -330,15 +426,14 @@ def backward_with_lists(q, k, v, o, lse, dout, lists: SparseLists, softmax_scale
     lse = lse.reshape(B, Hq, Sq).contiguous()
     if lse.dtype != torch.float32:
         raise TypeError("lse must be torch.float32")
-    dq = torch.empty_like(q)
-    dk = torch.empty_like(k)
-    dv = torch.empty_like(v)
+    dq, dk, dv = _new(q), _new(k), _new(v)
     n1, n2 = ctypes.c_uint64(0), ctypes.c_uint64(0)
     _cabi.check(_cabi.lib().fba_bwd_scratch_bytes(B, Hq, Sq, ctypes.byref(n1), ctypes.byref(n2)),
                 "fba_bwd_scratch_bytes")
-    lse_delta = torch.empty((n1.value // 4,), dtype=torch.float32, device=dev)
-    dq_accum = torch.empty((n2.value // 4,), dtype=torch.float32, device=dev)
-    lst = lists.bwd_list()
+    lse_delta = _new((n1.value // 4,), torch.float32, dev)
+    dq_accum = _new((n2.value // 4,), torch.float32, dev)
+    _monitor(dev).poll()
+    lst = lists.bwd_list(Hq, Hkv)
     with torch.cuda.device(dev):
         rc = _cabi.lib().fba_bwd_scaled(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
                                         dout.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
@@ -350,21 +445,55 @@ def backward_with_lists(q, k, v, o, lse, dout, lists: SparseLists, softmax_scale
     return dq, dk, dv
 
 
-def _fine_mask(block_mask, small_block_mask, use_small_block_mode):
-    return small_block_mask if (use_small_block_mode and small_block_mask is not None) else block_mask
+def _mask_ptr(m: Optional[torch.Tensor], like: torch.Tensor):
+    if m is None:
+        return None, None
+    if m.dtype != torch.bool:
+        raise TypeError("block_mask must be a torch.bool tensor")
+    if m.device != like.device:
+        raise RuntimeError("block_mask must be on the device of q (there is no CPU path)")
+    m = m.contiguous()
+    return m, m.data_ptr()
+
+
+def _attn_workspace(B, Hq, Hkv, Sq, Skv, q_block_size, kv_block_size, mask_dim, backward, dev):
+    n = ctypes.c_uint64(0)
+    _cabi.check(_cabi.lib().fba_attn_workspace_bytes(B, Hq, Hkv, Sq, Skv, q_block_size, kv_block_size, mask_dim,
+                                                     1 if backward else 0, ctypes.byref(n)),
+                "fba_attn_workspace_bytes")
+    return torch.empty((max(n.value, 256),), dtype=torch.uint8, device=dev), n.value
 
 
 def _flex_block_attn_forward(q, k, v, q_block_size, kv_block_size, block_mask, small_block_mask=None,
                              use_small_block_mode=False):
     """Same call shape as the reference pass-through (interface.py:6-8); returns (o, lse).
 
-    ``small_block_mask`` is the mask at [Sq/q_block, Skv/kv_block] granularity and is the one used
-    when ``use_small_block_mode`` is set (``block_mask`` is then the pooled mask, which this
-    implementation does not need).  ``lse`` is fp32 [B, H, Sq, 1], natural log.
+    Binds ``fba_attn_forward``, the C entry point that stands where the reference extension's
+    ``attn_forward`` stood: the bool masks go in as they are (``small_block_mask`` is the mask at
+    [Sq/q_block, Skv/kv_block] granularity and is the one used when ``use_small_block_mode`` is
+    set; ``block_mask`` is then the pooled mask, which this implementation does not need).
+    ``lse`` is fp32 [B, H, Sq, 1], natural log.
     """
-    mask = _fine_mask(block_mask, small_block_mask, use_small_block_mode)
-    lists = build_lists(mask, q_block_size, kv_block_size, q.shape[2], k.shape[2], need_bwd=False)
-    o, lse = forward_with_lists(q, k, v, lists)
+    _check_qkv(q, k, v)
+    B, Hq, Sq, _ = q.shape
+    Hkv, Skv = k.shape[1], k.shape[2]
+    dev = q.device
+    bm, bm_ptr = _mask_ptr(block_mask, q)
+    sm, sm_ptr = _mask_ptr(small_block_mask, q)
+    fine = sm if (use_small_block_mode and sm is not None) else bm
+    if fine is None or fine.dim() not in (2, 4):
+        raise ValueError("block_mask must have 2 or 4 dimensions")
+    o = _new(q)
+    lse = _new((B, Hq, Sq), torch.float32, dev)
+    ws, ws_bytes = _attn_workspace(B, Hq, Hkv, Sq, Skv, q_block_size, kv_block_size, fine.dim(), False, dev)
+    _monitor(dev).poll()
+    with torch.cuda.device(dev):
+        rc = _cabi.lib().fba_attn_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                          B, Hq, Hkv, Sq, Skv, q_block_size, kv_block_size, bm_ptr, sm_ptr,
+                                          fine.dim(), 1 if use_small_block_mode else 0, ws.data_ptr(), ws_bytes,
+                                          _status(dev).data_ptr(), _stream_ptr(dev))
+    _cabi.check(rc, "fba_attn_forward")
+    _maybe_check(dev)
     return o, lse.unsqueeze(-1)
 
 
@@ -372,13 +501,37 @@ def _flex_block_attn_backward(q, k, v, o, lse, do, q_block_size, kv_block_size, 
                               small_block_mask=None, use_small_block_mode=False):
     """Same call shape as the reference pass-through (interface.py:10-12); returns (dq, dk, dv).
 
-    Like the reference's, the masks arrive TRANSPOSED ([.., Skv/kv_block, Sq/q_block], reference
-    interface.py:85-86).
+    Binds ``fba_attn_backward``.  Like the reference's, the masks arrive TRANSPOSED
+    ([.., Skv/kv_block, Sq/q_block], reference interface.py:85-86).
     """
-    mask_t = _fine_mask(block_mask, small_block_mask, use_small_block_mode)
-    mask = mask_t.transpose(-1, -2).contiguous()
-    lists = build_lists(mask, q_block_size, kv_block_size, q.shape[2], k.shape[2], need_bwd=True)
-    return backward_with_lists(q, k, v, o, lse, do, lists)
+    _check_qkv(q, k, v)
+    B, Hq, Sq, _ = q.shape
+    Hkv, Skv = k.shape[1], k.shape[2]
+    dev = q.device
+    bm, bm_ptr = _mask_ptr(block_mask, q)
+    sm, sm_ptr = _mask_ptr(small_block_mask, q)
+    fine = sm if (use_small_block_mode and sm is not None) else bm
+    if fine is None or fine.dim() not in (2, 4):
+        raise ValueError("block_mask must have 2 or 4 dimensions")
+    if do.dtype != torch.bfloat16:
+        do = do.to(torch.bfloat16)
+    do = do.contiguous()
+    o = o.contiguous()
+    lse = lse.reshape(B, Hq, Sq).contiguous()
+    if lse.dtype != torch.float32:
+        raise TypeError("lse must be torch.float32")
+    dq, dk, dv = _new(q), _new(k), _new(v)
+    ws, ws_bytes = _attn_workspace(B, Hq, Hkv, Sq, Skv, q_block_size, kv_block_size, fine.dim(), True, dev)
+    _monitor(dev).poll()
+    with torch.cuda.device(dev):
+        rc = _cabi.lib().fba_attn_backward(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                           do.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                           B, Hq, Hkv, Sq, Skv, q_block_size, kv_block_size, bm_ptr, sm_ptr,
+                                           fine.dim(), 1 if use_small_block_mode else 0, ws.data_ptr(), ws_bytes,
+                                           _status(dev).data_ptr(), _stream_ptr(dev))
+    _cabi.check(rc, "fba_attn_backward")
+    _maybe_check(dev)
+    return dq, dk, dv
 
 
 class FlexBlockAttnFunc(torch.autograd.Function):

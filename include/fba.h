@@ -24,10 +24,14 @@
  * The softmax scale is 1/sqrt(128) (the reference's constant, .cu:177) unless an entry point takes one
  * explicitly; head_dim is fixed at 128 (.cu:833).
  *
- * Devices: every entry point that takes tensor pointers makes the device that owns them current on the
- * calling thread (cudaSetDevice) and leaves it current; callers juggling several devices restore their
- * own choice afterwards.  Host threads may call concurrently; fba_last_error() and the timing hook are
- * per thread.
+ * Devices: every entry point that takes tensor pointers runs on the device that owns them and puts the
+ * calling thread's previous CUDA context back before it returns (a thread that had none is left
+ * without one), so a call has no effect on the caller's device selection.  Host threads may call
+ * concurrently; fba_last_error() and the timing hook are per thread.
+ *
+ * Fixed limits (FBA_ERR_BAD_ARG / FBA_ERR_TOO_LARGE otherwise): head_dim 128; Sq >= 128 and Skv >= 128
+ * (the reference also accepts a sequence of one 64-row block, flex_block_attn_interface.py:19; pad
+ * such inputs to 128 rows with the extra keys masked off); B * Hq <= 65535 (grid y dimension).
  *
  * List format ("list" = fba_list_t): for list row r, entries idx[r * stride + e], e < cnt[r], are
  * ascending; unused slots hold -1.  `rows_per_bh` is the number of list rows of one (batch, head);
@@ -46,7 +50,7 @@
 extern "C" {
 #endif
 
-#define FBA_ABI_VERSION 1
+#define FBA_ABI_VERSION 2
 #define FBA_HEAD_DIM 128
 #define FBA_TILE 128
 
@@ -67,11 +71,28 @@ typedef struct fba_list {
     int32_t bh_stride;    /* rows_per_bh, or 0 when one list serves every (batch, head) */
     int32_t rows_div;     /* 128-row tiles per list row */
     int32_t sub;          /* 128-row tiles per entry */
+    const int32_t* order; /* NULL, or the work-item order from fba_fwd_order / fba_bwd_order */
 } fba_list_t;
 
 int fba_abi_version(void);
 /* Text of the most recent error on the calling thread ("" if none). */
 const char* fba_last_error(void);
+
+/*
+ * Read the 8 status words the attention kernels write when a bounded device-side wait gives up
+ * (synchronises `stream`).  FBA_OK if none did; otherwise FBA_ERR_TIMEOUT with the place in
+ * fba_last_error(), and the words are cleared.  No counterpart in the reference, whose kernels spin
+ * without a limit (its whole error handling is CHECK_CUDA_ERROR after the launch,
+ * flex_block_attn_h100.cu:1003, 1262).  Call it where the host synchronises anyway (once per step).
+ */
+int fba_check_status(uint32_t* status, void* stream);
+/*
+ * Self-test of that path: one toy CTA waits, with a budget of `limit_cycles` SM clocks, on a barrier
+ * nobody arrives at; the wait runs out, the kernel records (kernel 9, role 1, tag 777) in `status`
+ * and ends normally.  fba_check_status() afterwards returns FBA_ERR_TIMEOUT.  `waited_cycles`
+ * (device pointer, nullable) receives the clocks the wait took.
+ */
+int fba_selftest_wait_timeout(uint32_t* status, int64_t limit_cycles, uint64_t* waited_cycles, void* stream);
 
 /* Number of kernels this library has launched in this process (all threads). */
 uint64_t fba_launch_count(void);
@@ -108,6 +129,20 @@ int fba_build_tile_lists(const uint8_t* mask, int mask_dim, int B, int H, int nQ
                          int q_block, int kv_block, int Sq, int Skv, int32_t* fwd_idx,
                          int32_t* fwd_cnt, uint16_t* fwd_msk, int32_t* bwd_idx, int32_t* bwd_cnt,
                          uint16_t* bwd_msk, void* stream);
+
+/*
+ * Work-item order for the attention grids (no counterpart in the reference, whose CTAs take
+ * blockIdx order, flex_block_attn_h100.cu:924).  The forward launches one CTA per pair of 128-row
+ * query tiles, the backward one per 128-row key tile; list lengths differ, so both hand the items
+ * of each (batch, head) out longest first when `list->order` is set.  The order is the stable
+ * descending argsort of the item's work (sum of the list lengths it walks; backward: over the query
+ * heads of the kv head's group), integer and deterministic.
+ *   fba_fwd_order: order int32 [R, ceil(ceil(Sq/128)/2)],  R = B*Hq  (per-head list) or 1 (shared)
+ *   fba_bwd_order: order int32 [R, ceil(Skv/128)],         R = B*Hkv (per-head list) or 1 (shared)
+ * At most 12288 items per row (FBA_ERR_TOO_LARGE beyond; leave `order` NULL then).
+ */
+int fba_fwd_order(const fba_list_t* q2k, int B, int Hq, int Sq, int32_t* order, void* stream);
+int fba_bwd_order(const fba_list_t* k2q, int B, int Hq, int Hkv, int Skv, int32_t* order, void* stream);
 
 /*
  * Mask builders that emit lists directly (no counterpart in the reference: it advertises sliding-
@@ -182,6 +217,34 @@ int fba_bwd_scaled(const void* q, const void* k, const void* v, const void* o, c
                    const void* dout, void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int Sq,
                    int Skv, const fba_list_t* k2q, float softmax_scale, float* lse_delta,
                    float* dq_accum, uint32_t* status, void* stream);
+
+/*
+ * The reference extension's own call shape (reference attn.cpp:12-21 and
+ * flex_block_attn_h100.cu:810-818, 1009-1021): q, k, v (+ o, lse, dO), the two block sizes, the bool
+ * block mask(s) and use_small_block_mode in; o, lse / dq, dk, dv out.  Where the reference allocates
+ * its results and temporaries through torch inside the call (.cu:862-876, 1077-1093), the caller
+ * here passes the outputs and one 256-byte-aligned device workspace of fba_attn_workspace_bytes();
+ * mask compaction, work order and (backward) scratch all live there.  Stream-ordered; nothing is
+ * allocated.
+ *   block_mask / small_block_mask: uint8 (bool), mask_dim 2 or 4.  As in the reference,
+ *     small_block_mask is the mask at [Sq/q_block, Skv/kv_block] granularity and is the one used when
+ *     use_small_block_mode != 0 (block_mask, the pooled mask, is not needed then and may be NULL);
+ *     otherwise block_mask is used.
+ *   fba_attn_backward takes the masks TRANSPOSED ([.., Skv/kv_block, Sq/q_block]) like the reference
+ *     (flex_block_attn_interface.py:85-86).
+ *   lse: fp32 [B, Hq, Sq], natural log (the reference stores -sqrt(128) * LSE in [B, H, Sq, 1]).
+ */
+int fba_attn_workspace_bytes(int B, int Hq, int Hkv, int Sq, int Skv, int q_block_size, int kv_block_size,
+                             int mask_dim, int backward, uint64_t* bytes);
+int fba_attn_forward(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Hq, int Hkv,
+                     int Sq, int Skv, int q_block_size, int kv_block_size, const uint8_t* block_mask,
+                     const uint8_t* small_block_mask, int mask_dim, int use_small_block_mode, void* workspace,
+                     uint64_t workspace_bytes, uint32_t* status, void* stream);
+int fba_attn_backward(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                      const void* dout, void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int Sq, int Skv,
+                      int q_block_size, int kv_block_size, const uint8_t* block_mask_t,
+                      const uint8_t* small_block_mask_t, int mask_dim, int use_small_block_mode, void* workspace,
+                      uint64_t workspace_bytes, uint32_t* status, void* stream);
 
 /*
  * Backward for callers that cannot allocate device memory (no counterpart in the reference, whose

@@ -35,7 +35,7 @@ def test_header_symbols_are_exported(lib):
 
 
 def test_abi_version(lib):
-    assert lib.fba_abi_version() == 1
+    assert lib.fba_abi_version() == 2
 
 
 def test_bad_arguments_return_status_codes(lib):
@@ -46,11 +46,28 @@ def test_bad_arguments_return_status_codes(lib):
     assert n1.value == 2 * 384 * 2 * 4 and n2.value == 2 * 384 * 128 * 4
     assert lib.fba_bwd_scratch_bytes(0, 2, 300, ctypes.byref(n1), ctypes.byref(n2)) == -1
     assert lib.fba_fwd(None, None, None, None, None, 1, 1, 1, 128, 128, None, None, None) == -1
-    assert lib.fba_set_timing_events(3, None, None) == -1
+    assert lib.fba_set_timing_events(4, None, None) == -1
     assert lib.fba_set_timing_events(0, None, None) == 0
     # entry points added beside the reference's interface: argument checks come before any CUDA call
     assert lib.fba_fwd_scaled(None, None, None, None, None, 1, 1, 1, 128, 128, None, 0.1, None, None) == -1
     assert lib.fba_bwd_scaled(*([None] * 9), 1, 1, 1, 128, 128, None, 0.1, None, None, None, None) == -1
+    # the reference-shaped entry points, the work order, the status helpers
+    n = ctypes.c_uint64()
+    assert lib.fba_attn_workspace_bytes(1, 2, 2, 1536, 1536, 384, 384, 2, 0, ctypes.byref(n)) == 0
+    assert n.value == 256 * 3                              # 4x4 idx, 4 cnt, 6 order entries: one 256-byte slot each
+    assert lib.fba_attn_workspace_bytes(1, 2, 2, 1536, 1536, 384, 384, 2, 1, ctypes.byref(n)) == 0
+    assert n.value == 256 * 3 + 2 * 1536 * 2 * 4 + 2 * 1536 * 128 * 4
+    assert lib.fba_attn_workspace_bytes(1, 2, 2, 1536, 1536, 384, 384, 3, 0, ctypes.byref(n)) == -1
+    assert b"block_mask dim must be 2/4" in lib.fba_last_error()
+    assert lib.fba_attn_workspace_bytes(1, 2, 2, 1536, 1536, 100, 384, 2, 0, ctypes.byref(n)) == -1
+    assert lib.fba_attn_workspace_bytes(1, 2, 2, 1500, 1536, 384, 384, 2, 0, ctypes.byref(n)) == -1
+    assert lib.fba_attn_forward(*([None] * 5), 1, 1, 1, 128, 128, 128, 128, None, None, 2, 0, None, 0, None, None) == -1
+    assert lib.fba_attn_backward(*([None] * 9), 1, 1, 1, 128, 128, 128, 128, None, None, 2, 0, None, 0, None, None) == -1
+    assert lib.fba_fwd_order(None, 1, 1, 128, None, None) == -1
+    assert lib.fba_bwd_order(None, 1, 2, 1, 128, None, None) == -1
+    assert lib.fba_bwd_order(None, 1, 3, 2, 128, None, None) == -1
+    assert lib.fba_check_status(None, None) == -1
+    assert lib.fba_selftest_wait_timeout(None, 1000, None, None) == -1
     p = ctypes.c_void_p()
     assert lib.fba_peer_alloc(0, ctypes.byref(p)) == -1 and p.value is None
     assert lib.fba_peer_export(None, None) == -1 and lib.fba_peer_open(None, ctypes.byref(p)) == -1
@@ -67,3 +84,20 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.delenv("FBA_AUTO_BUILD", raising=False)
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         _cabi.lib()
+
+
+def test_setup_py_builds_the_library_into_the_package(tmp_path, lib):
+    """`setup.py build_py` (what `pip install .` runs) compiles for sm_100a and ships the .so."""
+    import subprocess
+    import sys
+
+    out = tmp_path / "lib"
+    r = subprocess.run([sys.executable, "setup.py", "-q", "build_py", "--build-lib", str(out)], cwd=ROOT,
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    pkg = out / "flex_block_attn_b200"
+    assert (pkg / "libfba_b200.so").exists() and (pkg / "interface.py").exists() and (pkg / "csrc" / "fba_fwd.cu").exists()
+    from flex_block_attn_b200.build import NVCC_FLAGS
+
+    archs = [f for f in NVCC_FLAGS if "arch=" in f or f.startswith("-arch")]
+    assert archs == ["arch=compute_100a,code=sm_100a"]

@@ -91,6 +91,39 @@ def _worker(rank, world, port, ret):
         assert torch.allclose(q2.grad, back(qt.grad), atol=1e-5)
         assert torch.allclose(k2.grad, back(kt.grad), atol=1e-5)
         assert torch.allclose(v2.grad, back(vt.grad), atol=1e-5)
+
+        # Two chained layers through ONE exchange whose results alias per-slot buffers, as the real
+        # PeerExchange's do: the second layer's exchanges overwrite the slots the first layer's q, k,
+        # v came from.  Autograd cannot see such stores, so the wiring must have kept private copies.
+        class AliasingExchange(GlooExchange):
+            def __init__(self):
+                self.to_head, self.to_seq = {}, {}
+
+            def seq_to_head(self, x, slot=0):
+                y = GlooExchange.seq_to_head(self, x, slot)
+                buf = self.to_head.setdefault(slot, torch.empty_like(y))
+                buf.copy_(y)
+                return buf
+
+            def head_to_seq(self, y, slot=0):
+                x = GlooExchange.head_to_seq(self, y, slot)
+                buf = self.to_seq.setdefault(slot, torch.empty_like(x))
+                buf.copy_(x)
+                return buf
+
+        ex = AliasingExchange()
+        q3, k3, v3 = (t.clone().requires_grad_() for t in rl[:3])
+        h1 = fd.ulysses_tile_major_attn(q3, k3, v3, 32, 32, lambda qh_, kh_: mask, ex, attn_fn=_cpu_attn)
+        h2 = fd.ulysses_tile_major_attn(h1, k3 * 0.5, v3 + 1.0, 32, 32, lambda qh_, kh_: mask, ex, attn_fn=_cpu_attn)
+        h2.backward(rl[3])
+        qt, kt, vt = (t[:, :, perm].clone().requires_grad_() for t in full[:3])
+        g1 = _cpu_attn(qt, kt, vt, 32, 32, mask)
+        g2 = _cpu_attn(g1, kt * 0.5, vt + 1.0, 32, 32, mask)
+        g2.backward(full[3][:, :, perm])
+        assert torch.allclose(h2, back(g2.detach()), atol=1e-5)
+        assert torch.allclose(q3.grad, back(qt.grad), atol=1e-5), "two layers sharing one exchange: dQ"
+        assert torch.allclose(k3.grad, back(kt.grad), atol=1e-5), "two layers sharing one exchange: dK"
+        assert torch.allclose(v3.grad, back(vt.grad), atol=1e-5), "two layers sharing one exchange: dV"
         ret[rank] = "ok"
     except Exception as e:  # pragma: no cover - surfaced through ret
         ret[rank] = f"{type(e).__name__}: {e}"

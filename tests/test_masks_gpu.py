@@ -1,9 +1,11 @@
-"""GPU: the list-emitting mask builders (fba_sta_index, fba_ssta_index) against the torch builders
-in flex_block_attn_b200/masks.py and the nonzero()-based list oracle."""
+"""GPU: the list-emitting mask builders (fba_sta_index, fba_ssta_index) against the mask definitions
+in oracle/mask_oracle.py and the nonzero()-based list oracle; the package's own torch builders
+(flex_block_attn_b200/masks.py) are held to the same definitions."""
 import pytest
 import torch
 
 from oracle import dense_oracle as orc
+from oracle import mask_oracle as mo
 from tests.util import rand_qkv
 
 pytestmark = pytest.mark.gpu
@@ -16,7 +18,8 @@ def test_sta_lists_equal_compacted_mask(grid, window):
     from flex_block_attn_b200 import masks
 
     lists = fba.sta_lists(grid, window, tile_tokens=384)
-    mask = masks.sta_mask(grid, window, device="cpu")
+    mask = mo.sta_mask(grid, window)
+    assert torch.equal(masks.sta_mask(grid, window, device="cpu"), mask)
     q2k_idx, q2k_cnt, k2q_idx, k2q_cnt = orc.block_index_oracle(mask)
     assert torch.equal(lists.fwd_idx.cpu(), q2k_idx) and torch.equal(lists.fwd_cnt.cpu(), q2k_cnt)
     assert torch.equal(lists.bwd_idx.cpu(), k2q_idx) and torch.equal(lists.bwd_cnt.cpu(), k2q_cnt)
@@ -49,26 +52,18 @@ def test_ssta_lists_match_torch_builder(B, Hq, Hkv, grid, qb, kb, topk):
     S = n_tiles * kb
     q, k, _, _ = rand_qkv(B, Hq, Hkv, S, S, seed=91 + topk, device="cuda")
     lists, mask = fba.ssta_lists(q, k, grid, qb, kb, topk=topk)
-    want = masks.ssta_mask(q, k, grid, qb, kb, topk=topk)
+    want = mo.ssta_mask(q, k, grid, qb, kb, topk=topk)
+    assert torch.equal(masks.ssta_mask(q, k, grid, qb, kb, topk=topk), want)
     assert mask.shape == want.shape and mask.dtype == torch.bool
     # the lists are exactly the compaction of the mask the kernel produced
     q2k_idx, q2k_cnt, k2q_idx, k2q_cnt = orc.block_index_oracle(mask.cpu())
     assert torch.equal(lists.fwd_idx.cpu(), q2k_idx) and torch.equal(lists.fwd_cnt.cpu(), q2k_cnt)
     assert torch.equal(lists.bwd_idx.cpu(), k2q_idx) and torch.equal(lists.bwd_cnt.cpu(), k2q_cnt)
-    # and the mask is the torch builder's; rows may differ only where pooled scores tie to within
-    # fp32 summation-order noise
-    diff_rows = (mask != want).any(-1)
-    if diff_rows.any():
-        qp = q.float().reshape(B, Hq, S // qb, qb, 128).mean(3)
-        kp = k.float().reshape(B, Hkv, S // kb, kb, 128).mean(3).repeat_interleave(Hq // Hkv, dim=1)
-        score = torch.matmul(qp, kp.transpose(-1, -2))
-        for b, h, r in diff_rows.nonzero().tolist():
-            a, w = mask[b, h, r], want[b, h, r]
-            only_a, only_w = (a & ~w).nonzero().flatten(), (w & ~a).nonzero().flatten()
-            assert len(only_a) == len(only_w)
-            sa, sw = score[b, h, r, only_a].sort().values, score[b, h, r, only_w].sort().values
-            assert torch.allclose(sa, sw, rtol=1e-4, atol=1e-5), "selection differs beyond a numerical tie"
-    assert diff_rows.float().mean().item() < 0.01
+    # and the mask is the definition's; a row may differ only where pooled scores tie to within fp32
+    # summation-order noise, every differing row is checked for that, and such rows must be rare
+    n_explained = mo.explain_selection_differences(mask, want, mo.pooled_scores(q, k, qb, kb))
+    assert n_explained == int((mask != want).any(-1).sum())
+    assert n_explained <= 0.01 * mask[..., 0].numel()
     assert bool((mask.sum(-1) >= min(topk, n_tiles)).all())
 
 
@@ -84,9 +79,11 @@ def test_moba_lists_match_torch_builder(qb, kb, topk):
     B, Hq, Hkv, S = 1, 4, 2, 3072
     q, k, v, do = rand_qkv(B, Hq, Hkv, S, S, seed=70 + topk, device="cuda")
     lists, mask = fba.moba_lists(q, k, qb, kb, topk)
-    want = masks.moba_topk_mask(q, k, qb, kb, topk)
+    want = mo.moba_topk_mask(q, k, qb, kb, topk)
+    assert torch.equal(masks.moba_topk_mask(q, k, qb, kb, topk), want)
     assert mask.shape == want.shape and bool((mask.sum(-1) == topk).all())
-    assert (mask != want).any(-1).float().mean().item() < 0.01
+    n_explained = mo.explain_selection_differences(mask, want, mo.pooled_scores(q, k, qb, kb))
+    assert n_explained <= 0.01 * mask[..., 0].numel()
     q2k_idx, q2k_cnt, k2q_idx, k2q_cnt = orc.block_index_oracle(mask.cpu())
     assert torch.equal(lists.fwd_idx.cpu(), q2k_idx) and torch.equal(lists.fwd_cnt.cpu(), q2k_cnt)
     assert torch.equal(lists.bwd_idx.cpu(), k2q_idx) and torch.equal(lists.bwd_cnt.cpu(), k2q_cnt)

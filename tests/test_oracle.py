@@ -110,3 +110,66 @@ def test_tile_words_by_loops():
     fi, fc, fm, bi, bc, bm = orc.tile_lists_oracle(m, q_block, kv_block, Sq, Skv)
     assert fi.shape == (n_mt, n_nt) and bi.shape == (n_nt, n_mt)
     assert int(fc.sum()) == int(bc.sum()) == int((w != 0).sum())
+
+
+# ------------------------------------------------------------------------------------------------
+# Structured-mask definitions and the work-item order (oracle/mask_oracle.py)
+# ------------------------------------------------------------------------------------------------
+def test_sta_mask_by_hand():
+    from oracle import mask_oracle as mo
+
+    # 1 x 2 x 3 grid of tiles, ids 0 1 2 / 3 4 5; window (0, 1, 1): neighbours in h and w
+    m = mo.sta_mask_loops((1, 2, 3), (0, 1, 1))
+    assert m.int().tolist() == [[1, 1, 0, 1, 1, 0], [1, 1, 1, 1, 1, 1], [0, 1, 1, 0, 1, 1],
+                                [1, 1, 0, 1, 1, 0], [1, 1, 1, 1, 1, 1], [0, 1, 1, 0, 1, 1]]
+    # window (0, 0, 1) on a 1 x 1 x 4 line is tridiagonal
+    assert mo.sta_mask_loops((1, 1, 4), (0, 0, 1)).int().tolist() == [[1, 1, 0, 0], [1, 1, 1, 0], [0, 1, 1, 1], [0, 0, 1, 1]]
+    for grid, win in (((3, 6, 10), (1, 1, 1)), ((2, 3, 4), (1, 0, 1)), ((4, 4, 4), (3, 3, 3))):
+        assert torch.equal(mo.sta_mask(grid, win), mo.sta_mask_loops(grid, win))
+
+
+def test_moba_and_ssta_masks_by_hand():
+    from oracle import mask_oracle as mo
+
+    # one head, 2 query blocks of 16 rows, 3 key blocks of 64 rows, every row of a block equal, so the
+    # pooled vectors are the rows themselves: q0 = e0, q1 = e1; k0 = 3 e0, k1 = 2 e0 + 5 e1, k2 = e1
+    D = 128
+    e = torch.eye(D)
+    q = torch.cat([e[0].expand(16, D), e[1].expand(16, D)])[None, None]
+    k = torch.cat([(3 * e[0]).expand(64, D), (2 * e[0] + 5 * e[1]).expand(64, D), e[1].expand(64, D)])[None, None]
+    score = mo.pooled_scores(q, k, 16, 64)
+    assert score[0, 0].tolist() == [[3.0, 2.0, 0.0], [0.0, 5.0, 1.0]]
+    assert mo.moba_topk_mask(q, k, 16, 64, 1)[0, 0].int().tolist() == [[1, 0, 0], [0, 1, 0]]
+    assert mo.moba_topk_mask(q, k, 16, 64, 2)[0, 0].int().tolist() == [[1, 1, 0], [0, 1, 1]]
+    assert torch.equal(mo.moba_topk_mask_loops(q, k, 16, 64, 2), mo.moba_topk_mask(q, k, 16, 64, 2))
+    # SSTA: kv_block 64 = one tile, q_block 16 -> both query blocks sit in tile 0 of a 1 x 1 x 3 line;
+    # window (0, 0, 1) adds tiles {0, 1} to both rows
+    m = mo.ssta_mask(q, k, (1, 1, 3), 16, 64, topk=1, window=(0, 0, 1))
+    assert m[0, 0].int().tolist() == [[1, 1, 0], [1, 1, 0]]
+    assert torch.equal(m, mo.ssta_mask_loops(q, k, (1, 1, 3), 16, 64, 1, (0, 0, 1)))
+    # random inputs, grouped-query heads: loops == vectorised
+    g = torch.Generator().manual_seed(1)
+    q = torch.randn((2, 4, 96, D), generator=g)
+    k = torch.randn((2, 2, 192, D), generator=g)
+    assert torch.equal(mo.moba_topk_mask_loops(q, k, 32, 64, 2), mo.moba_topk_mask(q, k, 32, 64, 2))
+    assert torch.equal(mo.ssta_mask_loops(q[:, :, :96], k, (1, 3, 1), 32, 64, 1, (0, 1, 0)),
+                       mo.ssta_mask(q[:, :, :96], k, (1, 3, 1), 32, 64, 1, (0, 1, 0)))
+    # the package's own torch builders state the same definitions
+    from flex_block_attn_b200 import masks
+
+    assert torch.equal(masks.moba_topk_mask(q, k, 32, 64, 2), mo.moba_topk_mask(q, k, 32, 64, 2))
+    assert torch.equal(masks.sta_mask((2, 3, 4), (1, 0, 1), device="cpu"), mo.sta_mask((2, 3, 4), (1, 0, 1)))
+
+
+def test_work_order_by_hand():
+    from oracle import mask_oracle as mo
+
+    # shared list, one tile per item: descending, ties keep index order
+    assert mo.work_order(torch.tensor([3, 1, 3, 0, 2, 2]), 6, False, 1, 1, 6, 1, 1).tolist() == [[0, 2, 4, 5, 1, 3]]
+    # forward items are tile pairs; 5 tiles, rows_div 1: keys (3+1, 3+0, 2) -> order 0, 1, 2
+    assert mo.work_order(torch.tensor([3, 1, 3, 0, 2]), 5, False, 1, 1, 5, 2, 1).tolist() == [[0, 1, 2]]
+    # 384-row blocks (rows_div 3), 6 tiles, pairs (0,1) (2,3) (4,5): keys (2a, a+b, 2b) with a=1, b=4
+    assert mo.work_order(torch.tensor([1, 4]), 2, False, 1, 3, 6, 2, 1).tolist() == [[2, 1, 0]]
+    # per-head list, two kv heads with two query heads each: keys are sums over the group
+    cnt = torch.tensor([1, 5,  4, 0,   2, 2,  0, 9])   # heads 0..3, 2 rows each
+    assert mo.work_order(cnt, 2, True, 2, 1, 2, 1, 2).tolist() == [[0, 1], [1, 0]]

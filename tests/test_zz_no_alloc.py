@@ -13,6 +13,7 @@ import ctypes
 import pytest
 import torch
 
+from oracle import dense_oracle as orc
 from tests.util import assert_close, bernoulli_mask, rand_qkv
 
 pytestmark = pytest.mark.gpu
@@ -59,11 +60,49 @@ def test_static_scratch_matches_fba_bwd_twice_in_a_row():
         scratch = (torch.empty(n1.value // 4, dtype=torch.float32, device="cuda"),
                    torch.empty(n2.value // 4, dtype=torch.float32, device="cuda"))
         want = _bwd("dynamic", q, k, v, o, lse, do, lists, scratch)
+        ref = orc.attention_slab(q.float(), k.float(), v.float(), mask, qb, kb, do.float())
         for rep in range(2):
             got = _bwd("static", q, k, v, o, lse, do, lists)
             assert torch.equal(got[1], want[1]), f"dK differs (shape {n}, call {rep})"
             assert torch.equal(got[2], want[2]), f"dV differs (shape {n}, call {rep})"
             assert_close(got[0].float(), want[0].float(), f"dQ (shape {n}, call {rep})", max_abs=1e-2)
+            for g, w, nm in zip(got, ref[2:], ("dQ", "dK", "dV")):
+                assert_close(g.float(), w, f"static scratch vs oracle {nm} (shape {n}, call {rep})")
+
+
+def test_static_scratch_at_exact_capacity_and_one_tile_beyond():
+    """B * Hq * ceil(Sq/128) * 128 == 131072 rows uses the array to its last byte (an off-by-one in
+    the split between its two regions would corrupt the last query tile of the last head, which
+    the oracle comparison on that head sees); one 128-row tile more is refused before any launch."""
+    import flex_block_attn_b200 as fba
+    from flex_block_attn_b200 import _cabi
+    from flex_block_attn_b200._cabi import FbaList
+
+    lib = _cabi.lib()
+    B, Hq, Hkv, Sq, Skv, qb, kb = 1, 8, 8, 16384, 1024, 128, 128
+    assert B * Hq * Sq == lib.fba_bwd_static_scratch_max_rows()
+    q, k, v, do = rand_qkv(B, Hq, Hkv, Sq, Skv, seed=77, device="cuda")
+    mask = bernoulli_mask((B, Hq, Sq // qb, Skv // kb), 0.5, 77).cuda()
+    lists = fba.build_lists(mask, qb, kb, Sq, Skv, need_bwd=True)
+    o, lse = fba.forward_with_lists(q, k, v, lists)
+    n1, n2 = ctypes.c_uint64(), ctypes.c_uint64()
+    assert lib.fba_bwd_scratch_bytes(B, Hq, Sq, ctypes.byref(n1), ctypes.byref(n2)) == 0
+    scratch = (torch.empty(n1.value // 4, dtype=torch.float32, device="cuda"),
+               torch.empty(n2.value // 4, dtype=torch.float32, device="cuda"))
+    want = _bwd("dynamic", q, k, v, o, lse, do, lists, scratch)
+    hs = slice(Hq - 1, Hq)   # the head whose scratch sits at the very end of the array
+    ref = orc.attention_slab(q[:, hs].float(), k[:, hs].float(), v[:, hs].float(), mask[:, hs], qb, kb, do[:, hs].float())
+    for rep in range(2):
+        got = _bwd("static", q, k, v, o, lse, do, lists)
+        assert torch.equal(got[1], want[1]) and torch.equal(got[2], want[2])
+        assert_close(got[0].float(), want[0].float(), f"dQ at capacity (call {rep})", max_abs=1e-2)
+        for g, w, nm in zip(got, ref[2:], ("dQ", "dK", "dV")):
+            assert_close(g[:, hs].float(), w, f"static scratch at capacity vs oracle {nm} (call {rep})")
+    x = torch.zeros(16, device="cuda")
+    p = x.data_ptr()
+    lst = FbaList()
+    rc = lib.fba_bwd_static_scratch(p, p, p, p, p, p, p, p, p, B, Hq, Hkv, Sq + 128, Skv, ctypes.byref(lst), p, None)
+    assert rc == -5 and b"exceeds the built-in scratch capacity" in lib.fba_last_error()
 
 
 def test_static_scratch_rejects_oversize():

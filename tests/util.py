@@ -60,11 +60,20 @@ def err_stats(got: torch.Tensor, want: torch.Tensor):
     return max_abs, cos
 
 
-def assert_close(got, want, what, max_abs=MAX_ABS, min_cos=MIN_COS, rel_to_max=True):
+PARITY_LOG: list = []   # (what, raw max-abs, cosine, max|want|) of every assert_close, in call order
+
+
+def assert_close(got, want, what, max_abs=MAX_ABS, min_cos=MIN_COS, rel_to_max=True, report=False):
     """max-abs (relative to max|want| when that exceeds 1, so large-magnitude inputs are judged on
-    the same bf16 footing) and cosine similarity."""
+    the same bf16 footing) and cosine similarity.  Returns (raw max-abs, cosine, max|want|); with
+    ``report`` the raw figures are also printed as one line (shown by ``pytest -s`` / ``-rP``)."""
     ma, cos = err_stats(got, want)
-    ref = max(1.0, want.detach().abs().max().item()) if rel_to_max else 1.0
+    mx = want.detach().abs().max().item()
+    ref = max(1.0, mx) if rel_to_max else 1.0
+    PARITY_LOG.append((what, ma, cos, mx))
+    if report:
+        print(f"PARITY {what}: max_abs={ma:.3e} cos={cos:.7f} max|ref|={mx:.3f} bound={max_abs * ref:.3e}")
     assert torch.isfinite(got.float()).all(), f"{what}: non-finite values"
     assert ma <= max_abs * ref, f"{what}: max-abs {ma:.4g} > {max_abs * ref:.4g} (cos {cos:.6f})"
     assert cos >= min_cos, f"{what}: cosine {cos:.6f} < {min_cos} (max-abs {ma:.4g})"
+    return ma, cos, mx
