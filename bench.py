@@ -1,25 +1,36 @@
 """Benchmark of the block-sparse attention hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload c3|c2|c4|c5] [--dq-mode atomic|qmajor]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-One "step" = one pass of the hot path over one batch of synthetic input: draw the block mask on
-the device, compact it into index lists (both directions), forward, backward.  The workload is the
-one the metric is quoted on: dynamic random block-sparse attention, B=1, H=24, D=128,
-q_block=kv_block=384, S=69120, Bernoulli(keep 0.4) per-(batch, head) mask with the diagonal
-forced on, q,k,v,dO ~ N(0,1) bf16 from a seed.  With N GPUs the 24 heads are split evenly over
-the ranks (no data-path collective; strong scaling: total work is fixed).
+One "step" = one pass of the hot path over one batch of synthetic input: build the block mask /
+index lists on the device, forward, backward.  The default workload (c3) is the one the metric is
+quoted on: dynamic random block-sparse attention, B=1, H=24, D=128, q_block=kv_block=384, S=69120,
+Bernoulli(keep 0.4) per-(batch, head) mask with the diagonal forced on, q,k,v,dO ~ N(0,1) bf16 from
+a seed.  The other benchmark configurations run through the same code with --workload:
+  c2  full attention, S=30720, 384-blocks, inputs N(0,1)*0.5
+  c4  3-D sliding-tile attention over 3x6x10 tiles of 384 tokens (S=69120), lists built without a mask
+  c5  SSTA (STA window + top-8 pooled q.k), q_block 128 / kv_block 384, B=2, S=69120
+With N GPUs the 24 heads are split evenly over the ranks (no data-path collective; strong scaling:
+total work is fixed).
 
 The printed line carries
   value      whole-job effective TFLOPS (14*qb*kb*D FLOPs per active block pair, active blocks
              only), inputs resident in HBM, CUDA events, max over ranks;
   e2e        the same metric through the public API (flex_block_attn_func + backward) with q, k, v,
-             dO copied from pinned host memory and a checksum read back inside the timed region;
+             dO copied from pinned host memory and O, dQ, dK, dV copied back to pinned host memory
+             inside the timed region (e2e_checksum_only: reading back a 4-float checksum instead);
   roofline   the backward main kernel (largest share of the step) against the measured dense
              bf16 peak, timed live with CUDA events recorded around that kernel alone;
   cpu_baseline  torch dense-masked SDPA (the reference's own oracle path) on the host cores, on a
-             bounded sample of the same workload.
-`--impl reference` times only that CPU path (the reference's CUDA kernels are Hopper-only and
+             bounded sample of the same workload;
+and, with N > 1 (default workload only),
+  multi_gpu_check  a small sequence-sharded problem through both Ulysses paths (NCCL exchange and
+             the fused peer-memory exchange) compared with the same rank computing it alone;
+  c5         configuration 5 with inputs arriving sequence-sharded: the sequence<->head exchange
+             timed on its own, beside mask/list building, forward and backward, for both paths.
+`--impl reference` times only the CPU path (the reference's CUDA kernels are Hopper-only and
 their ThunderKittens dependency is not vendored, so they cannot run on this machine).
 """
 from __future__ import annotations
@@ -27,6 +38,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -40,20 +52,11 @@ ROOT = Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-QB = KB = 384
 D = 128
-FLOPS_PER_PAIR_FWD = 4 * QB * KB * D
-FLOPS_PER_PAIR_BWD = 10 * QB * KB * D
-FLOPS_PER_PAIR = FLOPS_PER_PAIR_FWD + FLOPS_PER_PAIR_BWD
 METRIC = "fwd+bwd effective TFLOPS (active blocks), S=69120 sparse 0.6; % B200 bf16 peak"
-
-# DRAM traffic of the backward main kernel per active 384x384 block pair, from the ncu capture
-# summarised under profiles/ (backward kernel, S=23040 H=8 case): (dram__bytes_read.sum + dram__bytes_write.sum)
-# = 431.0 MB for the 11 805 pairs of the captured launch.  The bench workload is too large to capture
-# under the size rule, so `roofline.traffic` scales this figure by the pairs of a full launch; in
-# the captured case the dQ accumulator is L2-resident, at full size it is not, so the true figure is
-# higher than this proportional scaling.
-BWD_DRAM_BYTES_PER_PAIR = 431.0e6 / 11805
+STA_GRID = (3, 6, 10)          # tiles of 6x8x8 = 384 tokens over the 18x48x80 latent grid
+LATENT_GRID = (18, 48, 80)
+LATENT_TILE = (6, 8, 8)
 
 
 def parse_args():
@@ -62,11 +65,16 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--seq", type=int, default=69120)
+    ap.add_argument("--workload", choices=["c3", "c2", "c4", "c5"], default="c3")
+    ap.add_argument("--seq", type=int, default=None, help="sequence length (c3 sweep: 11520 ... 69120)")
     ap.add_argument("--heads", type=int, default=24)
     ap.add_argument("--keep", type=float, default=0.4)
+    ap.add_argument("--dq-mode", choices=["atomic", "qmajor"], default=None,
+                    help="dQ strategy of the backward (default: the library's default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-multi-gpu-extras", action="store_true",
+                    help="skip multi_gpu_check and the sequence-sharded c5 object at N > 1")
     return ap.parse_args()
 
 
@@ -77,6 +85,17 @@ def measured_peaks():
         return {"burst": float(d["bf16_tflops"]), "sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
                 "source": "measured"}
     return {"burst": 1590.0, "sustained": 1400.0, "source": "fallback"}
+
+
+def bwd_dram_bytes_per_pair():
+    """DRAM traffic of the backward main kernel per active 384x384 block pair, read from the committed
+    ncu summary (its `dram_bytes_per_active_pair = N` line); None if the summary does not carry one."""
+    best = None
+    for f in sorted((ROOT / "profiles").glob("fba_bwd_kernel_*.md")):
+        m = re.search(r"dram_bytes_per_active_pair\s*=\s*([0-9.eE+]+)", f.read_text())
+        if m:
+            best = (float(m.group(1)), f.name)
+    return best
 
 
 class ClockSampler:
@@ -149,22 +168,75 @@ def physical_gpu_index(local_rank: int) -> int:
 
 
 # ------------------------------------------------------------------------------------------------
+# Workloads
+# ------------------------------------------------------------------------------------------------
+class Workload:
+    """One benchmark configuration for the heads of one rank: shapes, input scale and the per-step
+    construction of the index lists (the "mask creation" that the step includes)."""
+
+    def __init__(self, name, args, Hl, rank, dev):
+        self.name, self.Hl, self.rank, self.dev = name, Hl, rank, dev
+        self.scale = 1.0
+        self.B = 1
+        if name == "c2":
+            self.S, self.qb, self.kb = args.seq or 30720, 384, 384
+            self.scale = 0.5
+            self.desc = f"C2 full attention fwd+bwd, B=1 H={args.heads} S={self.S} D=128 q_block=kv_block=384, all-ones 2-D mask"
+        elif name == "c3":
+            self.S, self.qb, self.kb = args.seq or 69120, 384, 384
+            self.keep = args.keep
+            self.desc = (f"C3 dynamic random block-sparse fwd+bwd, B=1 H={args.heads} S={self.S} D=128 q_block=kv_block=384 "
+                         f"Bernoulli(keep={args.keep})|diag per-(b,h) mask")
+        elif name == "c4":
+            self.S, self.qb, self.kb = 69120, 384, 384
+            self.desc = f"C4 sliding-tile attention fwd+bwd, B=1 H={args.heads} S=69120 D=128, 3x6x10 tiles of 384 tokens, window 3x3x3"
+        else:
+            self.B = 2
+            self.S, self.qb, self.kb = 69120, 128, 384
+            self.desc = (f"C5 SSTA (STA 3x3x3 window + top-8 pooled q.k) fwd+bwd, B=2 H={args.heads} S=69120 D=128 "
+                         "q_block=128 kv_block=384, per-(b,h) mask [540,180]")
+        self.flops_fwd = 4 * self.qb * self.kb * D
+        self.flops_bwd = 10 * self.qb * self.kb * D
+        self.flops = self.flops_fwd + self.flops_bwd
+        self.shape = (self.B, Hl, self.S, D)
+
+    def lists(self, fba, masks, step, q, k):
+        """-> (SparseLists, mask-or-None, active block pairs on this rank as a 0-d device tensor or int)."""
+        if self.name == "c2":
+            m = masks.full_mask(self.S // self.qb, self.S // self.kb, device=self.dev)
+            return fba.build_lists(m, self.qb, self.kb, self.S, self.S, need_bwd=True), m, m.numel() * self.B * self.Hl
+        if self.name == "c3":
+            nb = self.S // self.qb
+            m = masks.bernoulli_mask(1, self.Hl, nb, nb, self.keep, seed=7919 * (self.rank + 1) + step, device=self.dev)
+            return fba.build_lists(m, self.qb, self.kb, self.S, self.S, need_bwd=True), m, m.sum()
+        if self.name == "c4":
+            l = fba.sta_lists(STA_GRID, (1, 1, 1), tile_tokens=384, device=self.dev)
+            return l, None, l.fwd_cnt.sum() * (self.B * self.Hl)
+        l, m = fba.ssta_lists(q, k, STA_GRID, self.qb, self.kb, topk=8)
+        return l, m, m.sum()
+
+
+# ------------------------------------------------------------------------------------------------
 # CPU path (the reference's torch oracle) on a bounded sample of the workload
 # ------------------------------------------------------------------------------------------------
+QB_CPU = KB_CPU = 384
+FLOPS_PER_PAIR_CPU = 14 * QB_CPU * KB_CPU * D
+
+
 def cpu_sample_run(S: int, keep: float, n_qblocks: int, seed: int = 1234):
     """fwd+bwd of `n_qblocks` query blocks of one head against all S keys; returns (seconds, pairs)."""
     from oracle import dense_oracle as orc
 
     g = torch.Generator().manual_seed(seed)
-    nb = S // KB
-    q = torch.randn((1, 1, n_qblocks * QB, D), generator=g).requires_grad_()
+    nb = S // KB_CPU
+    q = torch.randn((1, 1, n_qblocks * QB_CPU, D), generator=g).requires_grad_()
     k = torch.randn((1, 1, S, D), generator=g).requires_grad_()
     v = torch.randn((1, 1, S, D), generator=g).requires_grad_()
-    do = torch.randn((1, 1, n_qblocks * QB, D), generator=g)
+    do = torch.randn((1, 1, n_qblocks * QB_CPU, D), generator=g)
     mask = torch.rand((n_qblocks, nb), generator=g) < keep
     mask[torch.arange(n_qblocks), torch.arange(n_qblocks)] = True
     t0 = time.perf_counter()
-    o = orc.sdpa_dense(q, k, v, mask, QB, KB)
+    o = orc.sdpa_dense(q, k, v, mask, QB_CPU, KB_CPU)
     o.backward(do)
     dt = time.perf_counter() - t0
     return dt, int(mask.sum())
@@ -184,14 +256,14 @@ def use_all_host_threads() -> int:
 def cpu_baseline(S: int, keep: float, target_s: float = 12.0):
     threads = use_all_host_threads()
     cpu_sample_run(min(S, 3840), keep, 1)  # warm-up of the torch CPU kernels
-    nq = 8 if S >= 8 * QB else max(1, S // QB)
+    nq = 8 if S >= 8 * QB_CPU else max(1, S // QB_CPU)
     dt, pairs = cpu_sample_run(S, keep, nq)
     reps = max(1, min(24, int(round(target_s / max(dt, 1e-3)))))
     for r in range(1, reps):
         d, p = cpu_sample_run(S, keep, nq, seed=1234 + r)
         dt += d
         pairs += p
-    tflops = pairs * FLOPS_PER_PAIR / dt / 1e12
+    tflops = pairs * FLOPS_PER_PAIR_CPU / dt / 1e12
     return {"value": tflops, "unit": "TFLOPS", "cores": threads, "kind": "port",
             "sample": f"torch F.scaled_dot_product_attention + dense token mask (the reference's oracle path), fp32, "
                       f"fwd+bwd of {reps} x {nq} query blocks of one head against all {S} keys of the S={S} keep={keep} workload, "
@@ -202,25 +274,190 @@ def run_reference_arm(args, rank, world):
     if rank != 0:
         return
     threads = use_all_host_threads()
+    S = args.seq or 69120
     times, pairs = [], 0
     for i in range(args.warmup + args.steps):
-        dt, pairs = cpu_sample_run(args.seq, args.keep, 1, seed=1234 + i)
+        dt, pairs = cpu_sample_run(S, args.keep, 1, seed=1234 + i)
         if i >= args.warmup:
             times.append(dt)
     ms = 1e3 * sum(times) / len(times)
-    val = pairs * FLOPS_PER_PAIR / (ms / 1e3) / 1e12
+    val = pairs * FLOPS_PER_PAIR_CPU / (ms / 1e3) / 1e12
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOPS", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"C3 dynamic random block-sparse, B=1 H={args.heads} S={args.seq} D=128 qb=kb=384 keep={args.keep}; "
+        "config": {"workload": f"C3 dynamic random block-sparse, B=1 H={args.heads} S={S} D=128 qb=kb=384 keep={args.keep}; "
                                "each step is a bounded sample: 1 query block of 1 head against all keys"},
         "cpu_baseline": {"value": val, "unit": "TFLOPS", "cores": threads, "kind": "port",
                          "sample": f"torch dense-masked SDPA fwd+bwd (the reference's oracle path; its CUDA kernels are sm_90a-only and "
-                                   f"their ThunderKittens dependency is absent), 1 query block x {args.seq} keys per step, {threads} threads"},
+                                   f"their ThunderKittens dependency is absent), 1 query block x {S} keys per step, {threads} threads"},
         "e2e": {"value": val, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# Multi-GPU extras (N > 1): correctness of both Ulysses paths, and configuration 5 sequence-sharded
+# ------------------------------------------------------------------------------------------------
+def _close(got, want, max_abs=1e-2, min_cos=0.9995):
+    g, w = got.float().flatten().double(), want.float().flatten().double()
+    ma = (g - w).abs().max().item()
+    cos = (g @ w).item() / max((g.norm() * w.norm()).item(), 1e-30)
+    return ma <= max_abs * max(1.0, w.abs().max().item()) and cos >= min_cos, ma, cos
+
+
+def multi_gpu_check(fba, fd, masks, dist, dev, rank, world):
+    """A small sequence-sharded problem (B=2, H=8, S=3072, q_block 128 / kv_block 384, SSTA mask)
+    through ulysses_flex_block_attn (NCCL exchange) and ulysses_tile_major_attn (fused peer-memory
+    exchange), each against this rank computing the whole problem alone: O, dK, dV bit for bit, dQ
+    (fp32 reductions in arrival order) by value."""
+    B, H, qb, kb = 2, 8, 128, 384
+    grid, tile = (2, 8, 192), (2, 8, 24)                 # S = 3072 tokens, 8 tiles of 384
+    tile_grid = (1, 1, 8)
+    S = grid[0] * grid[1] * grid[2]
+    Sl, Hl = S // world, H // world
+    sl, hs = slice(rank * Sl, (rank + 1) * Sl), slice(rank * Hl, (rank + 1) * Hl)
+    g = torch.Generator().manual_seed(4242)              # same seed on every rank: same full problem
+    raster = [torch.randn((B, S, H, D), generator=g).to(torch.bfloat16).to(dev) for _ in range(4)]   # q k v dO
+    tm = lambda t: masks.to_tile_major(t.contiguous(), grid, tile)       # [B, H, S, D] tile-major
+    rs = lambda t: masks.from_tile_major(t.contiguous(), grid, tile)     # [B, S, H, D] raster
+
+    def mask_fn(qh, kh):
+        return masks.ssta_mask(qh, kh, tile_grid, qb, kb, topk=2)
+
+    out = {}
+    # whole problem on this rank alone
+    full = [tm(t) for t in raster]
+    qf, kf, vf = (t.clone().requires_grad_() for t in full[:3])
+    of = fba.flex_block_attn_func(qf, kf, vf, qb, kb, mask_fn(qf, kf))
+    of.backward(full[3])
+    torch.cuda.synchronize()
+
+    def verdict(name, o, dq, dk, dv, want):
+        bad = []
+        for nm, g_, w_, exact in (("O", o, want[0], True), ("dK", dk, want[2], True), ("dV", dv, want[3], True),
+                                  ("dQ", dq, want[1], False)):
+            if exact:
+                if not torch.equal(g_, w_):
+                    bad.append(f"{nm} differs (max {(g_.float() - w_.float()).abs().max().item():.3g})")
+            else:
+                ok, ma, cos = _close(g_, w_)
+                if not ok:
+                    bad.append(f"{nm} max_abs {ma:.3g} cos {cos:.6f}")
+        t = torch.tensor([len(bad)], device=dev)
+        dist.all_reduce(t)
+        out[name] = "ok" if int(t.item()) == 0 else ("rank %d: %s" % (rank, "; ".join(bad)) if bad else "failed on another rank")
+
+    try:
+        ql, kl, vl = (t[:, :, sl].contiguous().requires_grad_() for t in full[:3])
+        o = fd.ulysses_flex_block_attn(ql, kl, vl, qb, kb, mask_fn)
+        o.backward(full[3][:, :, sl].contiguous())
+        torch.cuda.synchronize()
+        verdict("nccl_ulysses", o.detach(), ql.grad, kl.grad, vl.grad,
+                (of.detach()[:, :, sl], qf.grad[:, :, sl], kf.grad[:, :, sl], vf.grad[:, :, sl]))
+    except Exception as e:   # reported in the line; the run then exits non-zero
+        out["nccl_ulysses"] = f"{type(e).__name__}: {e}"
+    try:
+        ex = fd.PeerExchange(B, H, grid, tile, slots=4)
+        try:
+            q2, k2, v2 = (t[:, sl].contiguous().requires_grad_() for t in raster[:3])
+            o2 = fd.ulysses_tile_major_attn(q2, k2, v2, qb, kb, mask_fn, ex)
+            o2.backward(raster[3][:, sl].contiguous())
+            torch.cuda.synchronize()
+            verdict("peer_exchange", o2.detach(), q2.grad, k2.grad, v2.grad,
+                    (rs(of.detach())[:, sl], rs(qf.grad)[:, sl], rs(kf.grad)[:, sl], rs(vf.grad)[:, sl]))
+        finally:
+            ex.close()
+    except Exception as e:
+        out["peer_exchange"] = f"{type(e).__name__}: {e}"
+    fba.check_status(dev)
+    return out
+
+
+def c5_sequence_sharded(fba, fd, masks, dist, dev, rank, world, reps=3):
+    """Configuration 5 with inputs arriving sequence-sharded over the ranks (B=2, H=24, S=69120,
+    q_block 128 / kv_block 384, SSTA mask built after the exchange).  Every phase is timed on its
+    own with CUDA events (median of `reps`, max over ranks): the exchange towards the heads (q, k, v,
+    dO), mask + list building, forward, backward, the exchange back (O, dQ, dK, dV)."""
+    B, H, qb, kb = 2, 24, 128, 384
+    S = LATENT_GRID[0] * LATENT_GRID[1] * LATENT_GRID[2]
+    Sl, Hl = S // world, H // world
+    flops_pair = 14 * qb * kb * D
+    g = torch.Generator().manual_seed(9000 + rank)
+    mk = lambda shape: torch.randn(shape, generator=g).to(torch.bfloat16).to(dev)
+    bytes_tensor = B * Sl * H * D * 2                      # one local tensor
+    leaving = bytes_tensor * (world - 1) // world
+
+    def timed(fn):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        r = fn()
+        b.record()
+        return r, (a, b)
+
+    def reduce_ms(evs):
+        torch.cuda.synchronize()
+        t = torch.tensor([statistics.median(a.elapsed_time(b) for a, b in evs)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def run(path, to_head, to_seq, local):
+        phases = {k_: [] for k_ in ("a2a_in", "mask_lists", "fwd", "bwd", "a2a_out")}
+        pairs = None
+        for _ in range(reps + 1):                          # first pass warms up
+            dist.barrier()
+            heads, ev = timed(lambda: [to_head(t, i) for i, t in enumerate(local)])
+            phases["a2a_in"].append(ev)
+            qh, kh, vh, doh = heads
+            (lists, mask), ev = timed(lambda: fba.ssta_lists(qh, kh, STA_GRID, qb, kb, topk=8))
+            phases["mask_lists"].append(ev)
+            (o, lse), ev = timed(lambda: fba.forward_with_lists(qh, kh, vh, lists))
+            phases["fwd"].append(ev)
+            grads, ev = timed(lambda: fba.backward_with_lists(qh, kh, vh, o, lse, doh, lists))
+            phases["bwd"].append(ev)
+            _, ev = timed(lambda: [to_seq(t, i) for i, t in enumerate((o,) + tuple(grads))])
+            phases["a2a_out"].append(ev)
+            pairs = mask.sum()
+        ms = {k_: reduce_ms(v[1:]) for k_, v in phases.items()}
+        t = pairs.to(torch.float64).reshape(1)
+        dist.all_reduce(t)
+        total_pairs = float(t.item())
+        kern = ms["fwd"] + ms["bwd"]
+        allms = sum(ms.values())
+        return {"a2a_in_ms": ms["a2a_in"], "a2a_out_ms": ms["a2a_out"], "mask_lists_ms": ms["mask_lists"], "fwd_ms": ms["fwd"],
+                "bwd_ms": ms["bwd"], "a2a_bytes_leaving_gpu_per_direction": 4 * leaving,
+                "a2a_in_gbs_per_gpu": 4 * leaving / (ms["a2a_in"] / 1e3) / 1e9,
+                "a2a_out_gbs_per_gpu": 4 * leaving / (ms["a2a_out"] / 1e3) / 1e9,
+                "tflops_kernels_only": total_pairs * flops_pair / (kern / 1e3) / 1e12,
+                "tflops_with_exchange_and_mask": total_pairs * flops_pair / (allms / 1e3) / 1e12,
+                "active_block_pairs": total_pairs}
+
+    out = {"workload": f"C5 SSTA B=2 H=24 S={S} D=128 q_block=128 kv_block=384, inputs sequence-sharded [2, {Sl}, 24, 128] per GPU",
+           "timing": f"CUDA events per phase, median of {reps} after 1 warm-up pass, max over ranks; phases run back to back on one stream"}
+    try:
+        # NCCL path: head-major, tile-major chunks [B, H, S/P, D] exchanged by grouped send/recv
+        local = [mk((B, H, Sl, D)) for _ in range(4)]
+        out["nccl"] = run("nccl", lambda t, i: fd.seq_to_head(t), lambda t, i: fd.head_to_seq(t), local)
+        del local
+    except Exception as e:
+        out["nccl"] = {"error": f"{type(e).__name__}: {e}"}
+    torch.cuda.empty_cache()
+    try:
+        # fused path: native [B, S/P, H, D] raster chunks; one kernel does transpose + tile-major
+        # reorder + the exchange by peer stores over NVLink
+        ex = fd.PeerExchange(B, H, LATENT_GRID, LATENT_TILE, slots=4)
+        try:
+            local = [mk((B, Sl, H, D)) for _ in range(4)]
+            out["peer_exchange"] = run("peer", lambda t, i: ex.seq_to_head(t, i), lambda t, i: ex.head_to_seq(t, i), local)
+            out["peer_exchange"]["note"] = ("includes the [B,S,H,D] raster -> [B,H,S,D] tile-major layout change, which the NCCL "
+                                            "path's inputs have already had")
+        finally:
+            ex.close()
+    except Exception as e:
+        out["peer_exchange"] = {"error": f"{type(e).__name__}: {e}"}
+    fba.check_status(dev)
+    torch.cuda.empty_cache()
+    return out
 
 
 # ------------------------------------------------------------------------------------------------
@@ -232,11 +469,16 @@ def main():
     if args.impl == "reference":
         run_reference_arm(args, rank, world)
         return
+    if args.dq_mode:
+        os.environ["FBA_DQ_MODE"] = args.dq_mode
+    if world > 1:
+        # the fused exchange stores into peer memory with plain st.global; NVLS multicast is not used
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
 
     import torch.distributed as dist
     import flex_block_attn_b200 as fba
     from flex_block_attn_b200 import _cabi, masks
-    from flex_block_attn_b200.dist import head_shard
+    from flex_block_attn_b200 import dist as fd
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the operator)")
@@ -247,28 +489,24 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     lib = _cabi.lib()
 
-    S, H, keep = args.seq, args.heads, args.keep
-    hs = head_shard(H, world, rank)
+    H = args.heads
+    hs = fd.head_shard(H, world, rank)
     Hl = hs.stop - hs.start
-    nb = S // KB
+    wl = Workload(args.workload, args, Hl, rank, dev)
     gen = torch.Generator().manual_seed(1000 + rank)
-    shape = (1, Hl, S, D)
-    host = [torch.randn(shape, generator=gen).to(torch.bfloat16).pin_memory() for _ in range(4)]
+    shape = wl.shape
+    host = [(torch.randn(shape, generator=gen) * wl.scale).to(torch.bfloat16).pin_memory() for _ in range(4)]
     q, k, v, do = (t.to(dev) for t in host)
 
-    def make_mask(step):
-        return masks.bernoulli_mask(1, Hl, nb, nb, keep, seed=7919 * (rank + 1) + step, device=dev)
-
     def step_resident(step, hook=None):
-        mask = make_mask(step)
-        lists = fba.build_lists(mask, QB, KB, S, S, need_bwd=True)
+        lists, _, pairs = wl.lists(fba, masks, step, q, k)
         o, lse = fba.forward_with_lists(q, k, v, lists)
         if hook is not None:
             lib.fba_set_timing_events(2, hook[0].cuda_event, hook[1].cuda_event)
         out = fba.backward_with_lists(q, k, v, o, lse, do, lists)
         if hook is not None:
             lib.fba_set_timing_events(0, None, None)
-        return mask, out
+        return pairs, out
 
     def barrier():
         torch.cuda.synchronize()
@@ -304,7 +542,6 @@ def main():
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record(); b.record()
         hooks.append((a, b))
-    nnz = 0
     sampler = ClockSampler(physical_gpu_index(local_rank))
     barrier()
     if rank == 0:
@@ -312,26 +549,26 @@ def main():
     launches0 = lib.fba_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    masks_seen = []
+    pairs_seen = []
     for i in range(args.steps):
-        m, _ = step_resident(args.warmup + i, hooks[i])
-        masks_seen.append(m)
+        p, _ = step_resident(args.warmup + i, hooks[i])
+        pairs_seen.append(p)
     e1.record()
     barrier()
     launches = lib.fba_launch_count() - launches0
     fba.check_status(dev)
     ms_local = e0.elapsed_time(e1) / args.steps
     ms = max_over_ranks(ms_local)
-    nnz_local = sum(int(m.sum().item()) for m in masks_seen) / args.steps
+    nnz_local = sum(float(p) for p in pairs_seen) / args.steps
     nnz = sum_over_ranks(nnz_local)
-    value = nnz * FLOPS_PER_PAIR / (ms / 1e3) / 1e12
+    value = nnz * wl.flops / (ms / 1e3) / 1e12
     bwd_ms = statistics.mean(a.elapsed_time(b) for a, b in hooks)
-    del masks_seen
+    del pairs_seen
 
     # forward main kernel alone, a few extra steps (reported beside the roofline object)
     fwd_ms = None
     try:
-        lists = fba.build_lists(make_mask(0), QB, KB, S, S, need_bwd=False)
+        lists, _, _ = wl.lists(fba, masks, 0, q, k)
         fa, fb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         fa.record(); fb.record()
         lib.fba_set_timing_events(1, fa.cuda_event, fb.cuda_event)
@@ -342,20 +579,26 @@ def main():
             ts.append(fa.elapsed_time(fb))
         lib.fba_set_timing_events(0, None, None)
         fwd_ms = statistics.mean(ts)
+        del lists
     except Exception:
         lib.fba_set_timing_events(0, None, None)
 
     # ---------------------------------------------------------------- end to end through the API
     e2e = None
+    e2e_checksum = None
     if not args.no_e2e:
         copy_stream = torch.cuda.Stream(dev)
+        back_stream = torch.cuda.Stream(dev)
         # Two sets of device input buffers: while step s computes on one set, the inputs of step
         # s+1 are copied from pinned host memory into the other (every step's copy is inside the
-        # timed region; the first step's copy is fully exposed).
+        # timed region; the first step's copy is fully exposed).  The results of step s travel back
+        # to pinned host memory on a third stream while step s+1 computes; the last step's copy
+        # back is exposed, and the timed region ends only when it has landed.
         bufsets = [[torch.empty(shape, dtype=torch.bfloat16, device=dev) for _ in range(4)] for _ in range(2)]
         set_free = [None, None]     # event: compute that last read this set has finished
         set_ready = [None, None]    # events: (q,k,v copied, dO copied)
         result_host = torch.empty(4, dtype=torch.float32).pin_memory()
+        results_host = [torch.empty(shape, dtype=torch.bfloat16).pin_memory() for _ in range(4)]
 
         def issue_copy(slot):
             with torch.cuda.stream(copy_stream):
@@ -365,12 +608,13 @@ def main():
                     bufsets[slot][i].copy_(host[i], non_blocking=True)
                 qkv = torch.cuda.Event(); qkv.record(copy_stream)
                 bufsets[slot][3].copy_(host[3], non_blocking=True)
-                do = torch.cuda.Event(); do.record(copy_stream)
-            set_ready[slot] = (qkv, do)
+                dov = torch.cuda.Event(); dov.record(copy_stream)
+            set_ready[slot] = (qkv, dov)
 
-        def run_e2e(first_step, n):
+        def run_e2e(first_step, n, full_results):
             cur = torch.cuda.current_stream(dev)
             copy_stream.wait_stream(cur)
+            back_stream.wait_stream(cur)
             seen = []
             issue_copy(0)
             for j in range(n):
@@ -378,77 +622,119 @@ def main():
                 if j + 1 < n:
                     issue_copy(slot ^ 1)
                 bufs = bufsets[slot]
-                mask = make_mask(first_step + j)
                 cur.wait_event(set_ready[slot][0])
                 qq, kk, vv = (b.detach().requires_grad_() for b in bufs[:3])
-                o = fba.flex_block_attn_func(qq, kk, vv, QB, KB, mask)
+                lists, _, pairs = wl.lists(fba, masks, first_step + j, qq.detach(), kk.detach())
+                o = fba.flex_block_attn_func(qq, kk, vv, wl.qb, wl.kb, lists)
                 cur.wait_event(set_ready[slot][1])
                 o.backward(bufs[3])
-                res = torch.stack([t.sum(dtype=torch.float32) for t in (o.detach(), qq.grad, kk.grad, vv.grad)])   # one read pass each
-                result_host.copy_(res, non_blocking=True)
+                outs = (o.detach(), qq.grad, kk.grad, vv.grad)
+                if full_results:
+                    done = torch.cuda.Event(); done.record(cur)
+                    with torch.cuda.stream(back_stream):
+                        back_stream.wait_event(done)
+                        for t, h in zip(outs, results_host):
+                            h.copy_(t, non_blocking=True)
+                            t.record_stream(back_stream)
+                else:
+                    res = torch.stack([t.sum(dtype=torch.float32) for t in outs])   # one read pass each
+                    result_host.copy_(res, non_blocking=True)
                 ev = torch.cuda.Event(); ev.record(cur)
                 set_free[slot] = ev
-                seen.append(mask)
+                seen.append(pairs)
+            cur.wait_stream(back_stream)    # the timed region includes the last copy back
             return seen
 
-        run_e2e(0, max(2, min(args.warmup, 3)))
-        barrier()
-        n_e2e = max(2, min(args.steps, 10))
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0.record()
-        ms_seen = run_e2e(100, n_e2e)
-        t1.record()
-        barrier()
-        e_ms = max_over_ranks(t0.elapsed_time(t1) / n_e2e)
-        e_nnz = sum_over_ranks(sum(int(m.sum().item()) for m in ms_seen) / n_e2e)
-        e2e = {"value": e_nnz * FLOPS_PER_PAIR / (e_ms / 1e3) / 1e12, "unit": "TFLOPS",
-               "h2d_bytes_per_step": int(4 * host[0].numel() * 2 * world), "d2h_bytes_per_step": int(16 * world),
-               "ms_per_step": e_ms, "steps": n_e2e,
-               "note": "q,k,v,dO copied from pinned host memory every step (double-buffered: the copy for step s+1 overlaps the "
-                       "compute of step s; the first copy is exposed), flex_block_attn_func + backward through autograd, "
-                       "4-float checksum of o,dq,dk,dv read back every step"}
+        def measure(full_results):
+            run_e2e(0, max(2, min(args.warmup, 3)), full_results)
+            barrier()
+            n_e2e = max(2, min(args.steps, 10))
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            seen = run_e2e(100, n_e2e, full_results)
+            t1.record()
+            barrier()
+            e_ms = max_over_ranks(t0.elapsed_time(t1) / n_e2e)
+            e_nnz = sum_over_ranks(sum(float(p) for p in seen) / n_e2e)
+            nbytes = int(4 * host[0].numel() * 2 * world)
+            return {"value": e_nnz * wl.flops / (e_ms / 1e3) / 1e12, "unit": "TFLOPS", "h2d_bytes_per_step": nbytes,
+                    "d2h_bytes_per_step": nbytes if full_results else int(16 * world), "ms_per_step": e_ms, "steps": n_e2e}
+
+        e2e = measure(True)
+        e2e["note"] = ("q,k,v,dO copied from pinned host memory every step (double-buffered: the copy for step s+1 overlaps the "
+                       "compute of step s; the first copy is exposed); index lists built on the device; flex_block_attn_func + "
+                       "backward through autograd; O,dQ,dK,dV copied back to pinned host memory on a third stream (overlaps the "
+                       "next step; the last copy back is exposed and inside the timed region)")
+        e2e_checksum = measure(False)
+        e2e_checksum["note"] = "same, but a 4-float checksum of O,dQ,dK,dV is read back instead of the tensors"
         fba.check_status(dev)
+        del bufsets, results_host
 
     clocks = sampler.stop() if rank == 0 else None   # sampled over the resident and the end-to-end regions
     total_launches = sum_over_ranks(float(launches))
+
+    # ---------------------------------------------------------------- multi-GPU extras
+    mg_check = c5 = None
+    if world > 1 and args.workload == "c3" and not args.no_multi_gpu_extras:
+        del q, k, v, do, host
+        torch.cuda.empty_cache()
+        mg_check = multi_gpu_check(fba, fd, masks, dist, dev, rank, world)
+        c5 = c5_sequence_sharded(fba, fd, masks, dist, dev, rank, world)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
+        if mg_check and any(vv != "ok" for vv in mg_check.values()):
+            raise SystemExit(3)
         return
 
     peaks = measured_peaks()
-    bwd_flops = nnz_local * FLOPS_PER_PAIR_BWD
+    bwd_flops = nnz_local * wl.flops_bwd
     achieved = bwd_flops / (bwd_ms / 1e3) / 1e12
+    traffic = bwd_dram_bytes_per_pair()
+    pair_scale = (wl.qb * wl.kb) / (384.0 * 384.0)
     roofline = {
         "kernel": "fba_bwd_kernel", "bound": "tensor", "achieved": achieved, "peak": peaks["sustained"], "unit": "TFLOP/s",
         "frac": achieved / peaks["sustained"], "peak_kind": f"bf16_tflops_sustained of {peaks['source']} (kernel timed inside a long step)",
         "frac_of_burst_peak": achieved / peaks["burst"], "burst_peak": peaks["burst"],
         "ms_per_launch": bwd_ms, "flops_per_launch": bwd_flops,
-        "traffic": (BWD_DRAM_BYTES_PER_PAIR * nnz_local) if BWD_DRAM_BYTES_PER_PAIR else None,
-        "traffic_note": "bytes per launch, scaled per active pair from the ncu capture of a smaller case (profiles/)",
-        "share_of_step": bwd_ms / ms_local,
+        "traffic": (traffic[0] * pair_scale * nnz_local) if traffic else None,
+        "traffic_note": ("bytes per launch = dram_bytes_per_active_pair of profiles/%s (ncu capture of a smaller case) x the active "
+                         "pairs of this launch" % traffic[1]) if traffic else "no ncu summary with a per-pair figure found",
+        "share_of_step": bwd_ms / ms_local, "dq_mode": os.environ.get("FBA_DQ_MODE", "atomic"),
     }
     if fwd_ms:
-        fwd_ach = nnz_local * FLOPS_PER_PAIR_FWD / (fwd_ms / 1e3) / 1e12
+        fwd_ach = nnz_local * wl.flops_fwd / (fwd_ms / 1e3) / 1e12
         roofline["fwd_kernel"] = {"kernel": "fba_fwd_kernel", "ms_per_launch": fwd_ms, "achieved": fwd_ach,
                                   "frac": fwd_ach / peaks["sustained"], "frac_of_burst_peak": fwd_ach / peaks["burst"]}
+    per_rank_mb = 4 * shape[0] * shape[1] * shape[2] * shape[3] * 2 / 1e6
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": f"C3 dynamic random block-sparse fwd+bwd, B=1 H={H} S={S} D=128 q_block=kv_block=384 "
-                               f"Bernoulli(keep={keep})|diag per-(b,h) mask; mask draw + compaction inside the step; "
-                               f"heads split {Hl}/GPU", "l2": "inputs (4 x %.0f MB per rank) exceed the 126 MB L2" % (q.numel() * 2 / 1e6),
+        "config": {"workload": f"{wl.desc}; mask / list building inside the step; heads split {Hl}/GPU",
+                   "l2": ("working set per rank: q,k,v,dO,O,dQ,dK,dV = %.0f MB plus a %.0f MB fp32 dQ accumulator, streamed once per "
+                          "step (126 MB L2); no explicit flush between steps" % (2 * per_rank_mb, per_rank_mb / 4 * 2)),
                    "active_block_pairs": nnz, "pct_of_measured_burst_peak": 100 * value / (peaks["burst"] * world),
                    "pct_of_measured_sustained_peak": 100 * value / (peaks["sustained"] * world),
-                   "pct_of_nominal_2250": 100 * value / (2250.0 * world)},
-        "e2e": e2e, "gpu_launches": int(total_launches), "clocks": clocks, "roofline": roofline,
+                   "pct_of_nominal_2250": 100 * value / (2250.0 * world),
+                   "work_order": os.environ.get("FBA_WORK_ORDER", "1") != "0"},
+        "e2e": e2e, "e2e_checksum_only": e2e_checksum, "gpu_launches": int(total_launches), "clocks": clocks, "roofline": roofline,
     }
+    if clocks and clocks.get("sm_mhz"):
+        line["per_clock"] = {"tflops_per_gpu_per_ghz": value / world / (clocks["sm_mhz"] / 1e3),
+                             "note": "value / n_gpus / median SM clock of rank 0 during the timed regions"}
+    if mg_check is not None:
+        line["multi_gpu_check"] = mg_check
+    if c5 is not None:
+        line["c5"] = c5
     if not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline(S, keep)
+        line["cpu_baseline"] = cpu_baseline(args.seq or 69120, args.keep)
     if world > 1:
         dist.destroy_process_group()
     print(json.dumps(line), flush=True)   # last line of stdout
+    if mg_check and any(vv != "ok" for vv in mg_check.values()):
+        raise SystemExit(3)
 
 
 if __name__ == "__main__":

@@ -180,6 +180,9 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
                  "f"(d)
                  : "memory");
 }
+// kWithDq = false: the dK / dV-only variant that runs beside the query-major dQ pass
+// (fba_bwd_dq.cu): no dQ GEMM, no drain, no reductions.
+template <bool kWithDq>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -415,14 +418,16 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 if (!ok) break;
                 tc_fence_after();
                 if (it < 64) FBA_TRACE_REC(p.status, 1024 + it * 8 + 3);
-                mma_tile_mm(tDP, sDS, sK, false);     // dQ first: its drain overlaps the dK GEMM
-                umma_commit(bar(kBDqFull));
+                if (kWithDq) {
+                    mma_tile_mm(tDP, sDS, sK, false);     // dQ first: its drain overlaps the dK GEMM
+                    umma_commit(bar(kBDqFull));
+                }
                 mma_tile_km(tDK, sDS, sQ(st), it > 0);
                 umma_commit(bar(kBQEmpty + st));
                 if (it < 64) FBA_TRACE_REC(p.status, 1024 + it * 8 + 4);
                 if (it + 1 < n_total) {
                     wait(kBDoFull + (st ^ 1), ((it + 1) >> 1) & 1u, it, 214);
-                    wait(kBDqDrained, ph, it, 213);
+                    if (kWithDq) wait(kBDqDrained, ph, it, 213);   // else: dP^T(it) was consumed before dS^T(it) was announced
                     if (!ok) break;
                     tc_fence_after();
                     if (it < 64) FBA_TRACE_REC(p.status, 1024 + it * 8 + 5);
@@ -442,7 +447,7 @@ fba_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const uint32_t tdq = tDP + (static_cast<uint32_t>(quad * 32) << 16);
         int it = 0;
         bool ok = true;
-        for (int r = 0; r < hr && ok; ++r) {
+        for (int r = 0; r < hr && ok && kWithDq; ++r) {
             const long long lr = list_row(r);
             const int cnt = p.list.cnt[lr];
             const long long bq = bq0 + r;
@@ -662,13 +667,33 @@ extern "C" int fba_bwd_scratch_bytes(int B, int Hq, int Sq, uint64_t* lse_delta_
     return FBA_OK;
 }
 
-extern "C" int fba_bwd_scaled(const void* q, const void* k, const void* v, const void* o, const float* lse,
-                              const void* dout, void* dq, void* dk, void* dv, int B, int Hq, int Hkv,
-                              int Sq, int Skv, const fba_list_t* k2q, float softmax_scale, float* lse_delta,
-                              float* dq_accum, uint32_t* status, void* stream_) {
+namespace fba {
+int launch_bwd_dq(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_do,
+                  const CUtensorMap& tm_dq, const fba_list_t& q2k, const float* lse_delta, uint32_t* status,
+                  int n_mtiles, long long n_bhq, int Hq, int Hkv, float scale, cudaStream_t stream);
+}
+
+extern "C" int fba_bwd_ex(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                          const void* dout, void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int Sq,
+                          int Skv, const fba_list_t* k2q, const fba_list_t* q2k, float softmax_scale, int dq_mode,
+                          float* lse_delta, float* dq_accum, uint32_t* status, void* stream_) {
+    ProfRange range("fba_bwd");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    if (!q || !k || !v || !o || !lse || !dout || !dq || !dk || !dv || !lse_delta || !dq_accum || !status)
+    if (dq_mode != FBA_DQ_ATOMIC && dq_mode != FBA_DQ_QMAJOR)
+        return set_error(FBA_ERR_BAD_ARG, "fba_bwd: dq_mode must be FBA_DQ_ATOMIC or FBA_DQ_QMAJOR");
+    const bool qmajor = dq_mode == FBA_DQ_QMAJOR;
+    if (!q || !k || !v || !o || !lse || !dout || !dq || !dk || !dv || !lse_delta || !status ||
+        (!qmajor && !dq_accum))
         return set_error(FBA_ERR_BAD_ARG, "fba_bwd: null pointer argument");
+    if (qmajor) {
+        if (!q2k || !q2k->idx || !q2k->cnt || q2k->stride <= 0 || q2k->rows_per_bh <= 0 || q2k->rows_div <= 0 ||
+            q2k->sub <= 0 || (q2k->bh_stride != 0 && q2k->bh_stride != q2k->rows_per_bh))
+            return set_error(FBA_ERR_BAD_ARG, "fba_bwd: the query-major dQ pass needs a well-formed q2k list");
+        const int nm = (Sq + 127) / 128, nn = (Skv + 127) / 128;
+        if (static_cast<long long>(q2k->rows_per_bh) * q2k->rows_div < nm ||
+            static_cast<long long>(q2k->stride) * q2k->sub < nn || nn % q2k->sub != 0 || nm % q2k->rows_div != 0)
+            return set_error(FBA_ERR_BAD_ARG, "fba_bwd: q2k list does not cover the sequences");
+    }
     if (!(softmax_scale > 0.f) || !(softmax_scale < INFINITY))
         return set_error(FBA_ERR_BAD_ARG, "fba_bwd: softmax_scale must be positive and finite");
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || Sq <= 0 || Skv <= 0)
@@ -693,7 +718,7 @@ extern "C" int fba_bwd_scaled(const void* q, const void* k, const void* v, const
         return set_error(FBA_ERR_TOO_LARGE, "fba_bwd: B * Hq exceeds 65535");
 
     const long long n_bhq = static_cast<long long>(B) * Hq, n_bhk = static_cast<long long>(B) * Hkv;
-    CUtensorMap tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv;
+    CUtensorMap tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv, tm_dq;
     int rc;
     DeviceGuard guard;
     if ((rc = guard.bind(q)) != FBA_OK) return rc;
@@ -703,6 +728,7 @@ extern "C" int fba_bwd_scaled(const void* q, const void* k, const void* v, const
     if ((rc = make_tmap_bf16(&tm_do, dout, Sq, n_bhq, 128)) != FBA_OK) return rc;
     if ((rc = make_tmap_bf16(&tm_dk, dk, Skv, n_bhk, 128)) != FBA_OK) return rc;
     if ((rc = make_tmap_bf16(&tm_dv, dv, Skv, n_bhk, 128)) != FBA_OK) return rc;
+    if (qmajor && (rc = make_tmap_bf16(&tm_dq, dq, Sq, n_bhq, 128)) != FBA_OK) return rc;
 
     const int rows_pad = n_mtiles * 128;
     const long long total_rows = n_bhq * rows_pad;
@@ -716,13 +742,17 @@ extern "C" int fba_bwd_scaled(const void* q, const void* k, const void* v, const
             static_cast<uint32_t>(total_rows), softmax_scale);
         if ((rc = check_launch("bwd_prep_kernel")) != FBA_OK) return rc;
     }
-    if (cudaMemsetAsync(dq_accum, 0, static_cast<size_t>(total_rows) * 128 * sizeof(float), stream) != cudaSuccess) {
+    if (!qmajor &&
+        cudaMemsetAsync(dq_accum, 0, static_cast<size_t>(total_rows) * 128 * sizeof(float), stream) != cudaSuccess) {
         cudaGetLastError();
         return set_error(FBA_ERR_LAUNCH, "fba_bwd: cudaMemsetAsync failed");
     }
     {
-        cudaError_t e = cudaFuncSetAttribute(fba_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(fba_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(kBwdSmemBytes));
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(fba_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(kBwdSmemBytes));
         if (e != cudaSuccess) {
             cudaGetLastError();
             return set_error(FBA_ERR_LAUNCH, "fba_bwd: cannot raise the dynamic shared memory limit");
@@ -738,17 +768,31 @@ extern "C" int fba_bwd_scaled(const void* q, const void* k, const void* v, const
         p.scale = softmax_scale;
         dim3 grid(n_ntiles, static_cast<unsigned>(n_bhk));
         timing_mark(2, true, stream);
-        fba_bwd_kernel<<<grid, kBwdThreads, kBwdSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv, p);
+        if (qmajor)
+            fba_bwd_kernel<false><<<grid, kBwdThreads, kBwdSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv, p);
+        else
+            fba_bwd_kernel<true><<<grid, kBwdThreads, kBwdSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv, p);
         rc = check_launch("fba_bwd_kernel");
         timing_mark(2, false, stream);
         if (rc != FBA_OK) return rc;
     }
+    if (qmajor)
+        return launch_bwd_dq(tm_q, tm_k, tm_v, tm_do, tm_dq, *q2k, lse_delta, status, n_mtiles, n_bhq, Hq, Hkv,
+                             softmax_scale, stream);
     {
         dim3 grid(n_mtiles, static_cast<unsigned>(n_bhq));
         bwd_dq_convert_kernel<<<grid, 256, 0, stream>>>(dq_accum, static_cast<__nv_bfloat16*>(dq), Sq, n_mtiles);
         if ((rc = check_launch("bwd_dq_convert_kernel")) != FBA_OK) return rc;
     }
     return FBA_OK;
+}
+
+extern "C" int fba_bwd_scaled(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                              const void* dout, void* dq, void* dk, void* dv, int B, int Hq, int Hkv,
+                              int Sq, int Skv, const fba_list_t* k2q, float softmax_scale, float* lse_delta,
+                              float* dq_accum, uint32_t* status, void* stream) {
+    return fba_bwd_ex(q, k, v, o, lse, dout, dq, dk, dv, B, Hq, Hkv, Sq, Skv, k2q, nullptr, softmax_scale,
+                      FBA_DQ_ATOMIC, lse_delta, dq_accum, status, stream);
 }
 
 extern "C" int fba_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse,

@@ -498,6 +498,7 @@ static int check_list(const fba_list_t* l, const char* who) {
 static int fwd_impl(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Hq,
                     int Hkv, int Sq, int Skv, const fba_list_t* q2k, float softmax_scale, uint32_t* status,
                     void* stream_) {
+    ProfRange range("fba_fwd");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (!q || !k || !v || !o || !status)
         return set_error(FBA_ERR_BAD_ARG, "fba_fwd: null pointer argument");

@@ -412,10 +412,30 @@ def forward_with_lists(q, k, v, lists: SparseLists, softmax_scale=None, need_lse
     return o, lse
 
 
-def backward_with_lists(q, k, v, o, lse, dout, lists: SparseLists, softmax_scale=None):
+DQ_MODES = {"atomic": 0, "qmajor": 1}
+
+
+def default_dq_mode() -> str:
+    """dQ strategy used when a call does not name one: ``FBA_DQ_MODE`` (atomic | qmajor), else atomic."""
+    mode = os.environ.get("FBA_DQ_MODE", "atomic").lower()
+    if mode not in DQ_MODES:
+        raise ValueError(f"FBA_DQ_MODE must be one of {sorted(DQ_MODES)}, got {mode!r}")
+    return mode
+
+
+def backward_with_lists(q, k, v, o, lse, dout, lists: SparseLists, softmax_scale=None, dq_mode: Optional[str] = None):
     """Run the backward kernels; returns (dq, dk, dv) in bf16.  ``softmax_scale`` must be the
-    forward's."""
+    forward's.
+
+    ``dq_mode``: "atomic" (default) -- the key-major kernel adds dQ partials into an fp32
+    accumulator with vector reductions (fastest; dQ is reproducible to fp32 rounding only);
+    "qmajor" -- a second, query-major kernel accumulates dQ in tensor memory and writes it once
+    (bit-reproducible dQ, no fp32 accumulator; more tensor-core work).  None = ``FBA_DQ_MODE``.
+    """
     _check_qkv(q, k, v)
+    mode = default_dq_mode() if dq_mode is None else dq_mode
+    if mode not in DQ_MODES:
+        raise ValueError(f"dq_mode must be one of {sorted(DQ_MODES)}")
     B, Hq, Sq, _ = q.shape
     Hkv, Skv = k.shape[1], k.shape[2]
     dev = q.device
@@ -431,16 +451,18 @@ def backward_with_lists(q, k, v, o, lse, dout, lists: SparseLists, softmax_scale
     _cabi.check(_cabi.lib().fba_bwd_scratch_bytes(B, Hq, Sq, ctypes.byref(n1), ctypes.byref(n2)),
                 "fba_bwd_scratch_bytes")
     lse_delta = _new((n1.value // 4,), torch.float32, dev)
-    dq_accum = _new((n2.value // 4,), torch.float32, dev)
+    dq_accum = _new((n2.value // 4,), torch.float32, dev) if mode == "atomic" else None
     _monitor(dev).poll()
     lst = lists.bwd_list(Hq, Hkv)
+    q2k = lists.fwd_list(ordered=True) if mode == "qmajor" else None
     with torch.cuda.device(dev):
-        rc = _cabi.lib().fba_bwd_scaled(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
-                                        dout.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                                        B, Hq, Hkv, Sq, Skv, ctypes.byref(lst), _scale_of(softmax_scale),
-                                        lse_delta.data_ptr(), dq_accum.data_ptr(), _status(dev).data_ptr(),
-                                        _stream_ptr(dev))
-    _cabi.check(rc, "fba_bwd_scaled")
+        rc = _cabi.lib().fba_bwd_ex(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                    dout.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                    B, Hq, Hkv, Sq, Skv, ctypes.byref(lst),
+                                    ctypes.byref(q2k) if q2k is not None else None, _scale_of(softmax_scale),
+                                    DQ_MODES[mode], lse_delta.data_ptr(), _ptr(dq_accum), _status(dev).data_ptr(),
+                                    _stream_ptr(dev))
+    _cabi.check(rc, "fba_bwd_ex")
     _maybe_check(dev)
     return dq, dk, dv
 

@@ -102,7 +102,8 @@ uint64_t fba_launch_count(void);
  * fba_set_timing_events(which, e0, e1) the calling thread's later fba_fwd (which = 1) or fba_bwd
  * (which = 2) calls record the CUDA events e0 / e1 (cudaEvent_t) on their stream immediately
  * before / after the main attention kernel, so its duration can be read without the small
- * helper kernels around it.  which = 0 switches the hook off.
+ * helper kernels around it; which = 3 selects the query-major dQ kernel of FBA_DQ_QMAJOR.
+ * which = 0 switches the hook off.
  */
 int fba_set_timing_events(int which, void* start_event, void* stop_event);
 
@@ -217,6 +218,26 @@ int fba_bwd_scaled(const void* q, const void* k, const void* v, const void* o, c
                    const void* dout, void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int Sq,
                    int Skv, const fba_list_t* k2q, float softmax_scale, float* lse_delta,
                    float* dq_accum, uint32_t* status, void* stream);
+
+/*
+ * Backward with a choice of dQ strategy (the reference has only the first: its key-major kernel
+ * reduce-adds fp32 dQ tiles into global memory, flex_block_attn_h100.cu:700-718, 750-764).
+ *   FBA_DQ_ATOMIC  the key-major kernel adds each 128x128 dQ partial into the fp32 accumulator
+ *                  `dq_accum` with vector reductions; a conversion pass writes bf16 dQ.  `q2k` is
+ *                  not used (may be NULL).  dQ sums arrive in scheduling order: equal to fp32
+ *                  rounding, not bit-reproducible.
+ *   FBA_DQ_QMAJOR  a second, query-major kernel walks `q2k`, recomputes S and dP and accumulates
+ *                  dQ in tensor memory; the key-major kernel computes only dK and dV.  dQ is written
+ *                  once, in bf16, bit-reproducibly; `dq_accum` is not used (may be NULL) and only the
+ *                  small `lse_delta` scratch is needed.  Two more GEMMs per tile pair.
+ * fba_bwd_scaled(...) == fba_bwd_ex(..., q2k = NULL, ..., FBA_DQ_ATOMIC, ...).
+ */
+#define FBA_DQ_ATOMIC 0
+#define FBA_DQ_QMAJOR 1
+int fba_bwd_ex(const void* q, const void* k, const void* v, const void* o, const float* lse,
+               const void* dout, void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int Sq, int Skv,
+               const fba_list_t* k2q, const fba_list_t* q2k, float softmax_scale, int dq_mode,
+               float* lse_delta, float* dq_accum, uint32_t* status, void* stream);
 
 /*
  * The reference extension's own call shape (reference attn.cpp:12-21 and
