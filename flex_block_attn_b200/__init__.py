@@ -2,6 +2,7 @@
 ``flex_block_attn_func`` (same exported names as the reference's flex_block_attn/__init__.py:1-5)."""
 from .interface import (  # noqa: F401
     FlexBlockAttnFunc,
+    Fp8KVCache,
     SparseLists,
     _flex_block_attn_backward,
     _flex_block_attn_forward,
@@ -9,9 +10,11 @@ from .interface import (  # noqa: F401
     build_index,
     build_lists,
     check_status,
+    flex_block_attn_fp8kv,
     flex_block_attn_func,
     forward_with_lists,
     moba_lists,
+    quantize_kv,
     ssta_lists,
     sta_lists,
 )
@@ -30,4 +33,7 @@ __all__ = [
     "sta_lists",
     "ssta_lists",
     "moba_lists",
+    "Fp8KVCache",
+    "quantize_kv",
+    "flex_block_attn_fp8kv",
 ]

@@ -36,6 +36,8 @@ EXPORTED_SYMBOLS = (
     "fba_tile_major",
     "fba_fwd",
     "fba_fwd_scaled",
+    "fba_quantize_kv_e4m3",
+    "fba_fwd_fp8kv",
     "fba_bwd_scratch_bytes",
     "fba_bwd",
     "fba_bwd_scaled",
@@ -126,6 +128,10 @@ def lib() -> ctypes.CDLL:
     L.fba_fwd_scaled.restype = i32
     L.fba_fwd_scaled.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, ctypes.POINTER(FbaList),
                                  ctypes.c_float, vp, vp]
+    L.fba_quantize_kv_e4m3.restype = i32
+    L.fba_quantize_kv_e4m3.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp]
+    L.fba_fwd_fp8kv.restype = i32
+    L.fba_fwd_fp8kv.argtypes = [vp] * 5 + [i32, vp, vp] + [i32] * 5 + [ctypes.POINTER(FbaList), ctypes.c_float, vp, vp]
     L.fba_bwd_scratch_bytes.restype = i32
     L.fba_bwd_scratch_bytes.argtypes = [i32, i32, i32, ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]
     L.fba_bwd.restype = i32

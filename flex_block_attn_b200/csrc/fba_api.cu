@@ -129,6 +129,26 @@ int make_tmap_bf16(CUtensorMap* out, const void* base, int seq, long long n_bh, 
     return FBA_OK;
 }
 
+int make_tmap_u8(CUtensorMap* out, const void* base, long long inner, long long rows, long long n_bh) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return set_error(FBA_ERR_DRIVER, "cuTensorMapEncodeTiled is not available");
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || inner % 16 != 0)
+        return set_error(FBA_ERR_BAD_ARG, "8-bit tensor base address and row length must be multiples of 16 bytes");
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(n_bh)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(inner) * static_cast<cuuint64_t>(rows)};
+    cuuint32_t box[3] = {128, 128, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        char buf[128];
+        snprintf(buf, sizeof(buf), "cuTensorMapEncodeTiled (8-bit) failed with CUresult %d", (int)r);
+        return set_error(FBA_ERR_DRIVER, buf);
+    }
+    return FBA_OK;
+}
+
 }  // namespace fba
 
 extern "C" int fba_abi_version(void) { return FBA_ABI_VERSION; }

@@ -51,6 +51,10 @@ void timing_mark(int which, bool start, cudaStream_t stream);
 // `box_rows` rows x 1, 128-byte swizzle, out-of-range rows read as zero and are dropped on store.
 int make_tmap_bf16(CUtensorMap* out, const void* base, int seq, long long n_bh, int box_rows);
 
+// 3-D 8-bit tensor map over a [n_bh, rows, inner] byte tensor viewed as (inner, row, bh), box = 128 bytes x
+// 128 rows x 1, 128-byte swizzle: one box is one [128][128] e4m3 operand tile.
+int make_tmap_u8(CUtensorMap* out, const void* base, long long inner, long long rows, long long n_bh);
+
 // Status-word layout written by the attention kernels when a bounded wait gives up.
 //   [0] non-zero flag   [1] kernel id (1 fwd, 2 bwd, 3 dQ, 9 self-test)   [2] role id
 //   [3] blockIdx.x      [4] blockIdx.y      [5] iteration                [6] barrier tag

@@ -412,6 +412,77 @@ def forward_with_lists(q, k, v, lists: SparseLists, softmax_scale=None, need_lse
     return o, lse
 
 
+@dataclass
+class Fp8KVCache:
+    """Key / value cache in e4m3 with per-(batch, kv head, block) fp32 scales (``quantize_kv``).
+
+    ``k8``: uint8 [B, Hkv, Skv, 128]; ``v8t``: uint8 [B, Hkv, 128, Skv] (V is stored transposed);
+    ``k_scale`` / ``v_scale``: fp32 [B, Hkv, Skv / scale_block].
+    """
+
+    k8: torch.Tensor
+    v8t: torch.Tensor
+    k_scale: torch.Tensor
+    v_scale: torch.Tensor
+    scale_block: int
+
+    def dequantize(self):
+        """(k, v) in fp32, [B, Hkv, Skv, 128]: what the kernel's arithmetic stands for."""
+        B, Hkv, Skv, _ = self.k8.shape
+        k = self.k8.view(torch.float8_e4m3fn).float() * self.k_scale.repeat_interleave(self.scale_block, dim=-1)[..., None]
+        v = self.v8t.view(torch.float8_e4m3fn).float().transpose(-1, -2) * \
+            self.v_scale.repeat_interleave(self.scale_block, dim=-1)[..., None]
+        return k, v
+
+
+def quantize_kv(k: torch.Tensor, v: torch.Tensor, scale_block: int) -> Fp8KVCache:
+    """Quantise bf16 K and V [B, Hkv, Skv, 128] to e4m3 with one scale per block of ``scale_block``
+    key rows (a multiple of 128 that divides Skv)."""
+    _check_qkv(k, k, v)
+    B, Hkv, Skv, _ = k.shape
+    if scale_block % TILE != 0 or Skv % scale_block != 0:
+        raise ValueError("scale_block must be a multiple of 128 that divides the key length")
+    dev = k.device
+    k8 = torch.empty((B, Hkv, Skv, HEAD_DIM), dtype=torch.uint8, device=dev)
+    v8t = torch.empty((B, Hkv, HEAD_DIM, Skv), dtype=torch.uint8, device=dev)
+    ks = torch.empty((B, Hkv, Skv // scale_block), dtype=torch.float32, device=dev)
+    vs = torch.empty_like(ks)
+    with torch.cuda.device(dev):
+        lib = _cabi.lib()
+        _cabi.check(lib.fba_quantize_kv_e4m3(k.data_ptr(), k8.data_ptr(), ks.data_ptr(), B * Hkv, Skv, scale_block, 0,
+                                             _stream_ptr(dev)), "fba_quantize_kv_e4m3(k)")
+        _cabi.check(lib.fba_quantize_kv_e4m3(v.data_ptr(), v8t.data_ptr(), vs.data_ptr(), B * Hkv, Skv, scale_block, 1,
+                                             _stream_ptr(dev)), "fba_quantize_kv_e4m3(v)")
+    return Fp8KVCache(k8, v8t, ks, vs, scale_block)
+
+
+def flex_block_attn_fp8kv(q, cache: Fp8KVCache, q_block_size, kv_block_size, block_mask, softmax_scale=None,
+                          need_lse: bool = False):
+    """Inference forward over an e4m3 key / value cache: same arguments as ``flex_block_attn_func``
+    with ``cache`` in place of k and v.  Not differentiable.  Returns o (and lse when asked)."""
+    if not q.is_cuda or q.dtype != torch.bfloat16 or q.dim() != 4 or q.shape[-1] != HEAD_DIM or not q.is_contiguous():
+        raise ValueError("q must be a contiguous CUDA bf16 tensor [batch, heads, seq, 128]")
+    B, Hq, Sq, _ = q.shape
+    Bk, Hkv, Skv, _ = cache.k8.shape
+    if Bk != B or Hq % Hkv != 0:
+        raise ValueError("batch / head counts of q and the cache do not fit")
+    lists = block_mask if isinstance(block_mask, SparseLists) else \
+        build_lists(block_mask, q_block_size, kv_block_size, Sq, Skv, need_bwd=False)
+    dev = q.device
+    o = _new(q)
+    lse = _new((B, Hq, Sq), torch.float32, dev) if need_lse else None
+    _monitor(dev).poll()
+    lst = lists.fwd_list(ordered=True)
+    with torch.cuda.device(dev):
+        rc = _cabi.lib().fba_fwd_fp8kv(q.data_ptr(), cache.k8.data_ptr(), cache.v8t.data_ptr(), cache.k_scale.data_ptr(),
+                                       cache.v_scale.data_ptr(), cache.scale_block, o.data_ptr(), _ptr(lse), B, Hq, Hkv,
+                                       Sq, Skv, ctypes.byref(lst), _scale_of(softmax_scale), _status(dev).data_ptr(),
+                                       _stream_ptr(dev))
+    _cabi.check(rc, "fba_fwd_fp8kv")
+    _maybe_check(dev)
+    return (o, lse) if need_lse else o
+
+
 DQ_MODES = {"atomic": 0, "qmajor": 1}
 
 

@@ -200,6 +200,28 @@ int fba_fwd_scaled(const void* q, const void* k, const void* v, void* o, float* 
                    uint32_t* status, void* stream);
 
 /*
+ * Inference forward over an 8-bit key / value cache (no counterpart in the reference, which is bf16
+ * only, flex_block_attn_h100.cu:854-858).
+ *
+ * fba_quantize_kv_e4m3 writes the cache: x bf16 [n_bh, S, 128] -> e4m3 bytes with one fp32 scale per
+ * (bh, block of `scale_block` rows), scale = max|x| / 448 over the block (1 for an all-zero block),
+ * byte = e4m3(x / scale), round to nearest even.  transposed == 0: x8 is [n_bh, S, 128] (use for K);
+ * transposed != 0: x8 is [n_bh, 128, S] (use for V).  scales: fp32 [n_bh, S / scale_block].
+ * scale_block must be a multiple of 128 and divide S.
+ *
+ * fba_fwd_fp8kv: o = softmax(softmax_scale * q K^T on the listed blocks) V with K = k8 * k_scale,
+ * V = v8t^T * v_scale; q and o are bf16 like fba_fwd's, lse may be NULL.  Both GEMMs run in e4m3 on the
+ * tensor cores: q is quantised per row and the probabilities per element inside the kernel, so the
+ * result differs from the bf16 forward on the dequantised cache by 8-bit rounding of q and P
+ * (cosine >= 0.998 on the tested shapes).  Skv must be a multiple of scale_block.
+ */
+int fba_quantize_kv_e4m3(const void* x, uint8_t* x8, float* scales, int n_bh, int S, int scale_block,
+                         int transposed, void* stream);
+int fba_fwd_fp8kv(const void* q, const uint8_t* k8, const uint8_t* v8t, const float* k_scale,
+                  const float* v_scale, int scale_block, void* o, float* lse, int B, int Hq, int Hkv, int Sq,
+                  int Skv, const fba_list_t* q2k, float softmax_scale, uint32_t* status, void* stream);
+
+/*
  * Backward (replaces attention_backward, reference .cu:1009-1267, bwd_attend_prep_ker .cu:339-389
  * and bwd_attend_ker .cu:572-802).  Gradients come back in bf16.
  *   k2q      : key-major list (entries are query tiles)
