@@ -30,7 +30,7 @@ constexpr uint32_t kF8SmemRing = kF8SmemQ8 + 2 * kTile8Bytes;
 constexpr uint32_t kF8SmemBars = kF8SmemRing + kF8Stages * kTile8Bytes;
 constexpr uint32_t kF8SmemBytes = kF8SmemBars + 256 + 1024;   // + alignment slack
 constexpr uint32_t kIdescF8 = umma_idesc_e4m3(128, 128, 0, 0);
-constexpr float kE4m3Max = 448.f;
+constexpr float kInvE4m3Max = 1.0f / 448.0f;   // scale = amax * this (one fp32 multiplication, reproducible anywhere)
 
 enum F8Bar : uint32_t {
     kF8QFull = 0,                          // 2: bf16 Q tile landed
@@ -308,7 +308,7 @@ fba_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                         amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
                     }
                 }
-                const float qs = amax > 0.f ? amax / kE4m3Max : 1.f;
+                const float qs = amax > 0.f ? amax * kInvE4m3Max : 1.f;
                 const float inv = 1.f / qs;
                 c_row = p.scale_log2 * qs;
                 uint8_t* q8row = base_ptr + kF8SmemQ8 + static_cast<uint32_t>(t) * kTile8Bytes + static_cast<uint32_t>(row) * 128u;
@@ -484,7 +484,7 @@ fba_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
 // ------------------------------------------------------------------------------------------
 // Cache writer: bf16 [n_bh, S, 128] -> e4m3 with one fp32 scale per (bh, block of `block` rows),
-// scale = amax / 448 (1 for an all-zero block), value = x / scale.  transposed == 0 writes
+// scale = amax * fp32(1/448) (1 for an all-zero block), value = x * (1 / scale).  transposed == 0 writes
 // [n_bh, S, 128]; transposed != 0 writes [n_bh, 128, S] (the layout the forward wants for V).
 // One CTA per (128-row tile, bh); the block's amax is recomputed per tile from the whole block
 // (blocks are a few tiles), so there is no second pass over a scratch buffer.
@@ -516,7 +516,7 @@ __global__ void __launch_bounds__(256) quantize_kv_kernel(const __nv_bfloat16* _
     amax = red[0];
 #pragma unroll
     for (int j = 1; j < 8; ++j) amax = fmaxf(amax, red[j]);
-    const float scale = amax > 0.f ? amax / kE4m3Max : 1.f;
+    const float scale = amax > 0.f ? amax * kInvE4m3Max : 1.f;
     const float inv = 1.f / scale;
     if (threadIdx.x == 0 && tile_idx % tiles_per_block == 0) scales[static_cast<long long>(bh) * n_sblocks + sblk] = scale;
 

@@ -204,8 +204,8 @@ int fba_fwd_scaled(const void* q, const void* k, const void* v, void* o, float* 
  * only, flex_block_attn_h100.cu:854-858).
  *
  * fba_quantize_kv_e4m3 writes the cache: x bf16 [n_bh, S, 128] -> e4m3 bytes with one fp32 scale per
- * (bh, block of `scale_block` rows), scale = max|x| / 448 over the block (1 for an all-zero block),
- * byte = e4m3(x / scale), round to nearest even.  transposed == 0: x8 is [n_bh, S, 128] (use for K);
+ * (bh, block of `scale_block` rows), scale = max|x| * fp32(1/448) over the block (1 for an all-zero
+ * block), byte = e4m3(x * (1 / scale)), round to nearest even, saturating.  transposed == 0: x8 is [n_bh, S, 128] (use for K);
  * transposed != 0: x8 is [n_bh, 128, S] (use for V).  scales: fp32 [n_bh, S / scale_block].
  * scale_block must be a multiple of 128 and divide S.
  *
@@ -213,7 +213,7 @@ int fba_fwd_scaled(const void* q, const void* k, const void* v, void* o, float* 
  * V = v8t^T * v_scale; q and o are bf16 like fba_fwd's, lse may be NULL.  Both GEMMs run in e4m3 on the
  * tensor cores: q is quantised per row and the probabilities per element inside the kernel, so the
  * result differs from the bf16 forward on the dequantised cache by 8-bit rounding of q and P
- * (cosine >= 0.998 on the tested shapes).  Skv must be a multiple of scale_block.
+ * (cosine >= 0.999 against the oracle on the dequantised cache on the tested shapes).  Skv must be a multiple of scale_block.
  */
 int fba_quantize_kv_e4m3(const void* x, uint8_t* x8, float* scales, int n_bh, int S, int scale_block,
                          int transposed, void* stream);

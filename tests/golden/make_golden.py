@@ -1,7 +1,7 @@
 """Generate the golden vectors under tests/golden/ by running the REFERENCE's own oracle code on CPU.
 
 Usage (in a container that has the reference checkout):
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path to the reference checkout>
 
 The reference's test module cannot be imported as a whole (it imports the CUDA extension and runs
 a CUDA test at import time), so this script parses it with ``ast`` and executes only the function
@@ -85,7 +85,9 @@ def run_bench_style_case(fns, seq_len, block, keep):
 
 
 def main():
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path to the reference checkout>")
+    ref = Path(sys.argv[1])
     test_fns = load_functions(ref / "test" / "test_flex_block_attn.py",
                               ["create_mask", "torch_attn_test", "generate_tensor"])
     bench_fns = load_functions(ref / "benchmark" / "utils" / "utils.py",

@@ -4,7 +4,7 @@ The cache writer is integer / byte work and is held bit-exactly to the oracle's 
 forward is compared with the oracle evaluated on the DEQUANTISED cache and the per-row e4m3 round
 trip of q, i.e. on exactly the operands the kernel's arithmetic stands for; what remains is the
 kernel's 8-bit rounding of the probabilities and fp32 summation order.  Tolerance for that:
-cosine >= 0.998 and max-abs <= 5e-2 * max(1, max|expected|), stated here because it is wider than
+cosine >= 0.999 and max-abs <= 5e-2 * max(1, max|expected|), stated here because it is wider than
 the bf16 kernels' 2e-2 / 0.9995 (e4m3 keeps 3 mantissa bits).
 """
 import pytest
@@ -14,7 +14,7 @@ from oracle import dense_oracle as orc
 from tests.util import assert_close, bernoulli_mask, rand_qkv
 
 pytestmark = pytest.mark.gpu
-FP8_MAX_ABS, FP8_MIN_COS = 5e-2, 0.998
+FP8_MAX_ABS, FP8_MIN_COS = 5e-2, 0.999
 
 
 @pytest.mark.parametrize("S,block,scale", [(768, 128, 1.0), (1536, 384, 1.0), (1536, 768, 3.0), (256, 256, 0.01)])
