@@ -71,6 +71,8 @@ def parse_args():
     ap.add_argument("--keep", type=float, default=0.4)
     ap.add_argument("--dq-mode", choices=["atomic", "qmajor"], default=None,
                     help="dQ strategy of the backward (default: the library's default)")
+    ap.add_argument("--fp8", action="store_true",
+                    help="also time the inference forward over an e4m3 key/value cache (reported as fp8_fwd)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-multi-gpu-extras", action="store_true",
@@ -583,6 +585,30 @@ def main():
     except Exception:
         lib.fba_set_timing_events(0, None, None)
 
+    # inference forward over an e4m3 key / value cache, same lists (optional)
+    fp8_fwd = None
+    if args.fp8:
+        cache = fba.quantize_kv(k, v, wl.kb)
+        lists, _, pairs = wl.lists(fba, masks, 0, q, k)
+        fa, fb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        fa.record(); fb.record()
+        lib.fba_set_timing_events(1, fa.cuda_event, fb.cuda_event)
+        ts8, ts16 = [], []
+        for _ in range(5):
+            fba.flex_block_attn_fp8kv(q, cache, wl.qb, wl.kb, lists)
+            torch.cuda.synchronize()
+            ts8.append(fa.elapsed_time(fb))
+            fba.forward_with_lists(q, k, v, lists, need_lse=False)
+            torch.cuda.synchronize()
+            ts16.append(fa.elapsed_time(fb))
+        lib.fba_set_timing_events(0, None, None)
+        t8, t16 = statistics.median(ts8[1:]), statistics.median(ts16[1:])
+        fl = float(pairs) * wl.flops_fwd
+        fp8_fwd = {"ms_fp8": t8, "ms_bf16": t16, "tflops_fp8": fl / (t8 / 1e3) / 1e12, "tflops_bf16": fl / (t16 / 1e3) / 1e12,
+                   "note": "forward kernel alone (CUDA events around it), this rank's heads, median of 4; K/V cache in e4m3 with "
+                           f"one scale per {wl.kb} keys, q quantised in the kernel"}
+        del cache, lists
+
     # ---------------------------------------------------------------- end to end through the API
     e2e = None
     e2e_checksum = None
@@ -626,6 +652,12 @@ def main():
                 qq, kk, vv = (b.detach().requires_grad_() for b in bufs[:3])
                 lists, _, pairs = wl.lists(fba, masks, first_step + j, qq.detach(), kk.detach())
                 o = fba.flex_block_attn_func(qq, kk, vv, wl.qb, wl.kb, lists)
+                if full_results:       # O is final after the forward: it travels back while the backward runs
+                    fwd_done = torch.cuda.Event(); fwd_done.record(cur)
+                    with torch.cuda.stream(back_stream):
+                        back_stream.wait_event(fwd_done)
+                        results_host[0].copy_(o.detach(), non_blocking=True)
+                        o.record_stream(back_stream)
                 cur.wait_event(set_ready[slot][1])
                 o.backward(bufs[3])
                 outs = (o.detach(), qq.grad, kk.grad, vv.grad)
@@ -633,7 +665,7 @@ def main():
                     done = torch.cuda.Event(); done.record(cur)
                     with torch.cuda.stream(back_stream):
                         back_stream.wait_event(done)
-                        for t, h in zip(outs, results_host):
+                        for t, h in zip(outs[1:], results_host[1:]):
                             h.copy_(t, non_blocking=True)
                             t.record_stream(back_stream)
                 else:
@@ -724,6 +756,8 @@ def main():
     if clocks and clocks.get("sm_mhz"):
         line["per_clock"] = {"tflops_per_gpu_per_ghz": value / world / (clocks["sm_mhz"] / 1e3),
                              "note": "value / n_gpus / median SM clock of rank 0 during the timed regions"}
+    if fp8_fwd is not None:
+        line["fp8_fwd"] = fp8_fwd
     if mg_check is not None:
         line["multi_gpu_check"] = mg_check
     if c5 is not None:

@@ -394,9 +394,12 @@ fba_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             l2a.y *= alpha;
             l2b.x *= alpha;
             l2b.y *= alpha;
-            const float neg_off = have_off ? -off : 0.f;
-            // P (times the relative V scale) goes to TMEM as e4m3, four keys per column, in four
-            // pieces of 32 keys; a piece is announced once its TMEM store has completed.
+            // P goes to TMEM as e4m3 times the relative V scale pv <= 1, which is folded into the
+            // exponent (exp2(x + log2 pv) = pv * exp2(x)); the row sum wants the unscaled P, so this
+            // step's sum of scaled values is divided by pv once.  Four keys per column, four pieces
+            // of 32 keys; a piece is announced once its TMEM store has completed.
+            const float neg_off = (have_off ? -off : 0.f) + lg2_approx(pv);
+            float2 sa = make_float2(0.f, 0.f), sb = make_float2(0.f, 0.f);
             uint32_t pk[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
@@ -404,13 +407,13 @@ fba_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #pragma unroll
                 for (int x = 0; x < 4; ++x) e[x] = ex2_approx(fmaf(__uint_as_float(u[4 * j + x]), c, neg_off));
                 if (j & 1) {
-                    l2b.x += e[0] + e[2];
-                    l2b.y += e[1] + e[3];
+                    sb.x += e[0] + e[2];
+                    sb.y += e[1] + e[3];
                 } else {
-                    l2a.x += e[0] + e[2];
-                    l2a.y += e[1] + e[3];
+                    sa.x += e[0] + e[2];
+                    sa.y += e[1] + e[3];
                 }
-                pk[j] = pack_e4m3x4(e[0] * pv, e[1] * pv, e[2] * pv, e[3] * pv);
+                pk[j] = pack_e4m3x4(e[0], e[1], e[2], e[3]);
                 if ((j & 7) == 7) {
                     const int q = j >> 3;
                     tmem_st8(tS + 8u * q, reinterpret_cast<uint32_t(&)[8]>(pk[8 * q]));
@@ -419,6 +422,11 @@ fba_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                     mbar_arrive(bar(kF8P + 4 * t + q));
                 }
             }
+            const float inv_pv = 1.f / pv;
+            l2a.x = fmaf(sa.x, inv_pv, l2a.x);
+            l2a.y = fmaf(sa.y, inv_pv, l2a.y);
+            l2b.x = fmaf(sb.x, inv_pv, l2b.x);
+            l2b.y = fmaf(sb.y, inv_pv, l2b.y);
         }
         const float l = (l2a.x + l2a.y) + (l2b.x + l2b.y);
 
