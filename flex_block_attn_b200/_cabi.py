@@ -42,6 +42,7 @@ EXPORTED_SYMBOLS = (
     "fba_bwd",
     "fba_bwd_scaled",
     "fba_bwd_ex",
+    "fba_set_bwd_kernel",
     "fba_bwd_static_scratch_max_rows",
     "fba_bwd_static_scratch",
     "fba_peer_alloc",
@@ -141,6 +142,8 @@ def lib() -> ctypes.CDLL:
     L.fba_bwd_ex.restype = i32
     L.fba_bwd_ex.argtypes = [vp] * 9 + [i32] * 5 + [ctypes.POINTER(FbaList), ctypes.POINTER(FbaList), ctypes.c_float, i32,
                                                      vp, vp, vp, vp]
+    L.fba_set_bwd_kernel.restype = i32
+    L.fba_set_bwd_kernel.argtypes = [i32]
     L.fba_bwd_static_scratch_max_rows.restype = ctypes.c_uint64
     L.fba_bwd_static_scratch_max_rows.argtypes = []
     L.fba_bwd_static_scratch.restype = i32

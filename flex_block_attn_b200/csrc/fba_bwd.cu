@@ -27,7 +27,13 @@
 //
 // Shared memory: K, V resident (64 KiB); Q double-buffered with its (lse2, delta) rows (64 + 2 KiB);
 // dO double-buffered (64 KiB); dS^T (32 KiB).
+#include <stdlib.h>
+
 #include "fba_common.cuh"
+
+#ifndef FBA_BWD_KERNEL_DEFAULT
+#define FBA_BWD_KERNEL_DEFAULT 1
+#endif
 
 namespace fba {
 
@@ -668,9 +674,35 @@ extern "C" int fba_bwd_scratch_bytes(int B, int Hq, int Sq, uint64_t* lse_delta_
 }
 
 namespace fba {
+int launch_bwd_v2(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_do,
+                  const CUtensorMap& tm_dk, const CUtensorMap& tm_dv, const fba_list_t& k2q, const float* lse_delta,
+                  float* dq_accum, uint32_t* status, int n_mtiles, int n_ntiles, long long n_bhk, int Hq, int Hkv,
+                  float scale, cudaStream_t stream);
+
+// Which key-major kernel the default dQ mode runs: 1 = score tile transposed, lane = key row
+// (fba_bwd_kernel<1>); 2 = lane = query row (fba_bwd_v2_kernel).  Set by fba_set_bwd_kernel() or, before
+// the first call, by the environment variable FBA_BWD_KERNEL.
+static int g_bwd_kernel = 0;   // 0 = not chosen yet
+static int bwd_kernel_choice() {
+    int c = __atomic_load_n(&g_bwd_kernel, __ATOMIC_RELAXED);
+    if (c == 0) {
+        const char* e = getenv("FBA_BWD_KERNEL");
+        c = (e && e[0] == '2' && e[1] == 0) ? 2 : (e && e[0] == '1' && e[1] == 0) ? 1 : FBA_BWD_KERNEL_DEFAULT;
+        __atomic_store_n(&g_bwd_kernel, c, __ATOMIC_RELAXED);
+    }
+    return c;
+}
+
 int launch_bwd_dq(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_do,
                   const CUtensorMap& tm_dq, const fba_list_t& q2k, const float* lse_delta, uint32_t* status,
                   int n_mtiles, long long n_bhq, int Hq, int Hkv, float scale, cudaStream_t stream);
+}
+
+extern "C" int fba_set_bwd_kernel(int which) {
+    if (which != 1 && which != 2) return set_error(FBA_ERR_BAD_ARG, "fba_set_bwd_kernel: which must be 1 or 2");
+    const int prev = bwd_kernel_choice();
+    __atomic_store_n(&g_bwd_kernel, which, __ATOMIC_RELAXED);
+    return prev;
 }
 
 extern "C" int fba_bwd_ex(const void* q, const void* k, const void* v, const void* o, const float* lse,
@@ -767,14 +799,20 @@ extern "C" int fba_bwd_ex(const void* q, const void* k, const void* v, const voi
         p.Hkv = Hkv;
         p.scale = softmax_scale;
         dim3 grid(n_ntiles, static_cast<unsigned>(n_bhk));
-        timing_mark(2, true, stream);
-        if (qmajor)
-            fba_bwd_kernel<false><<<grid, kBwdThreads, kBwdSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv, p);
-        else
-            fba_bwd_kernel<true><<<grid, kBwdThreads, kBwdSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv, p);
-        rc = check_launch("fba_bwd_kernel");
-        timing_mark(2, false, stream);
-        if (rc != FBA_OK) return rc;
+        if (!qmajor && bwd_kernel_choice() == 2) {
+            rc = launch_bwd_v2(tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv, *k2q, lse_delta, dq_accum, status, n_mtiles,
+                               n_ntiles, n_bhk, Hq, Hkv, softmax_scale, stream);
+            if (rc != FBA_OK) return rc;
+        } else {
+            timing_mark(2, true, stream);
+            if (qmajor)
+                fba_bwd_kernel<false><<<grid, kBwdThreads, kBwdSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv, p);
+            else
+                fba_bwd_kernel<true><<<grid, kBwdThreads, kBwdSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv, p);
+            rc = check_launch("fba_bwd_kernel");
+            timing_mark(2, false, stream);
+            if (rc != FBA_OK) return rc;
+        }
     }
     if (qmajor)
         return launch_bwd_dq(tm_q, tm_k, tm_v, tm_do, tm_dq, *q2k, lse_delta, status, n_mtiles, n_bhq, Hq, Hkv,

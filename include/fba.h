@@ -256,6 +256,15 @@ int fba_bwd_scaled(const void* q, const void* k, const void* v, const void* o, c
  */
 #define FBA_DQ_ATOMIC 0
 #define FBA_DQ_QMAJOR 1
+/*
+ * Two interchangeable key-major kernels exist for FBA_DQ_ATOMIC (same results to fp32 summation
+ * order in dK / dV, same scratch): 1 keeps the score tile transposed (tensor-memory lane = key row,
+ * P^T feeds dV straight from tensor memory), 2 keeps it upright (lane = query row: per-row log-sum-exp
+ * and delta are scalars, P and dS go through shared memory).  1 is the default because it measures
+ * 4-5 % faster on B200; `FBA_BWD_KERNEL=2` in the environment, or this call, selects the other.
+ * Returns the previous choice (1 or 2), or FBA_ERR_BAD_ARG.  Process-wide.
+ */
+int fba_set_bwd_kernel(int which);
 int fba_bwd_ex(const void* q, const void* k, const void* v, const void* o, const float* lse,
                const void* dout, void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int Sq, int Skv,
                const fba_list_t* k2q, const fba_list_t* q2k, float softmax_scale, int dq_mode,

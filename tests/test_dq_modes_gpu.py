@@ -91,3 +91,26 @@ def test_autograd_uses_the_mode_from_the_environment(monkeypatch):
     monkeypatch.setenv("FBA_DQ_MODE", "bogus")
     with pytest.raises(ValueError):
         fba.interface.default_dq_mode()
+
+
+@pytest.mark.parametrize("case", ["c1_2d", "c3_like", "c5_like", "gqa", "cross", "tile_mask_64_192", "tile_mask_16_64",
+                                  "ragged", "odd_tiles"])
+def test_alternative_key_major_kernel(case):
+    """The second key-major kernel (query-row orientation, selectable with fba_set_bwd_kernel(2) or
+    FBA_BWD_KERNEL=2) against the oracle, and against the default kernel."""
+    from flex_block_attn_b200 import _cabi
+
+    lib = _cabi.lib()
+    prev = lib.fba_set_bwd_kernel(2)
+    try:
+        assert prev in (1, 2)
+        (q, k, v, do, mask, qb, kb), got = _run(case, "atomic")
+    finally:
+        assert lib.fba_set_bwd_kernel(prev) == 2
+    want = orc.attention_slab(q.float(), k.float(), v.float(), mask, qb, kb, do.float())
+    for g, w, nm in zip(got, want[2:], ("dQ", "dK", "dV")):
+        assert_close(g.float(), w, f"kernel 2 {case} {nm}")
+    _, ref = _run(case, "atomic")
+    for g, w, nm in zip(got, ref, ("dQ", "dK", "dV")):
+        assert_close(g.float(), w.float(), f"kernel 2 vs 1 {case} {nm}", max_abs=1e-2)
+    assert lib.fba_set_bwd_kernel(3) == -1
