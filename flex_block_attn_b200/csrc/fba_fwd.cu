@@ -511,8 +511,6 @@ static int fwd_impl(const void* q, const void* k, const void* v, void* o, float*
         return set_error(FBA_ERR_BAD_ARG, "fba_fwd: sequence lengths below 128 are not supported");
     int rc = check_list(q2k, "fba_fwd: malformed q2k list");
     if (rc != FBA_OK) return rc;
-    DeviceGuard guard;
-    if ((rc = guard.bind(q)) != FBA_OK) return rc;
     const int n_mtiles = (Sq + 127) / 128;
     const int n_ntiles = (Skv + 127) / 128;
     if (static_cast<long long>(q2k->rows_per_bh) * q2k->rows_div < n_mtiles ||
@@ -525,6 +523,8 @@ static int fwd_impl(const void* q, const void* k, const void* v, void* o, float*
                          "fba_fwd: ceil(Skv/128) must be a multiple of q2k->sub and ceil(Sq/128) of q2k->rows_div");
     if (static_cast<long long>(B) * Hq > 65535)
         return set_error(FBA_ERR_TOO_LARGE, "fba_fwd: B * Hq exceeds 65535");
+    DeviceGuard guard;
+    if ((rc = guard.bind(q)) != FBA_OK) return rc;
 
     CUtensorMap tm_q, tm_k, tm_v, tm_o;
     if ((rc = make_tmap_bf16(&tm_q, q, Sq, static_cast<long long>(B) * Hq, 128)) != FBA_OK) return rc;

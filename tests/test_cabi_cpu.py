@@ -76,6 +76,45 @@ def test_bad_arguments_return_status_codes(lib):
     assert b"fba_peer_exchange" in lib.fba_last_error()
 
 
+def test_list_geometry_is_checked_before_any_device_work(lib):
+    """A list whose entries / rows stand for groups of tiles must cover whole groups: a sequence that
+    ends inside a group would make the kernels touch tiles (and backward scratch) past its end.
+    The pointers below are never dereferenced: the checks answer first."""
+    from flex_block_attn_b200._cabi import FbaList
+
+    fake = ctypes.c_void_p(0x1000)
+    def lst(stride, rows, rows_div, sub):
+        return FbaList(0x1000, 0x1000, None, stride, rows, rows, rows_div, sub)
+    # forward: Skv = 640 -> 5 key tiles, entries of 3 tiles (kv_block 384) do not divide it
+    l = lst(2, 2, 1, 3)
+    assert lib.fba_fwd(fake, fake, fake, fake, fake, 1, 1, 1, 256, 640, ctypes.byref(l), fake, None) == -1
+    assert b"multiple of q2k->sub" in lib.fba_last_error()
+    # forward: Sq = 640 -> 5 query tiles, list rows of 3 tiles do not divide it
+    l = lst(2, 2, 3, 1)
+    assert lib.fba_fwd(fake, fake, fake, fake, fake, 1, 1, 1, 640, 256, ctypes.byref(l), fake, None) == -1
+    # a list that does not cover the sequence at all
+    l = lst(1, 1, 1, 1)
+    assert lib.fba_fwd(fake, fake, fake, fake, fake, 1, 1, 1, 256, 256, ctypes.byref(l), fake, None) == -1
+    assert b"does not cover" in lib.fba_last_error()
+    # backward: the mirrored pair for the key-major list
+    l = lst(2, 2, 1, 3)
+    args = [fake] * 9 + [1, 1, 1, 640, 256, ctypes.byref(l), fake, fake, fake, None]
+    assert lib.fba_bwd(*args) == -1 and b"multiple of k2q->sub" in lib.fba_last_error()
+    l = lst(2, 2, 3, 1)
+    args = [fake] * 9 + [1, 1, 1, 256, 640, ctypes.byref(l), fake, fake, fake, None]
+    assert lib.fba_bwd(*args) == -1
+    # sizes the kernels do not support, and the dQ mode
+    l = lst(1, 1, 1, 1)
+    assert lib.fba_fwd(fake, fake, fake, fake, fake, 1, 1, 1, 64, 64, ctypes.byref(l), fake, None) == -1
+    assert b"below 128" in lib.fba_last_error()
+    assert lib.fba_fwd(fake, fake, fake, fake, fake, 1024, 64, 64, 128, 128, ctypes.byref(l), fake, None) == -5
+    args = [fake] * 9 + [1, 1, 1, 128, 128, ctypes.byref(l), None, ctypes.c_float(0.1), 7, fake, fake, fake, None]
+    assert lib.fba_bwd_ex(*args) == -1 and b"dq_mode" in lib.fba_last_error()
+    args[17] = 1   # FBA_DQ_QMAJOR without a q2k list
+    assert lib.fba_bwd_ex(*args) == -1 and b"q2k" in lib.fba_last_error()
+    assert lib.fba_set_bwd_kernel(0) == -1
+
+
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     from flex_block_attn_b200 import _cabi
 
