@@ -118,7 +118,7 @@ class ClockSampler:
             self.path = f.name
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "50"], stdout=f, stderr=subprocess.DEVNULL)
+                 "--format=csv,noheader,nounits", "-lms", "20"], stdout=f, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
@@ -557,6 +557,7 @@ def main():
         pairs_seen.append(p)
     e1.record()
     barrier()
+    clocks = sampler.stop() if rank == 0 else None     # sampled over the device-resident timed region only
     launches = lib.fba_launch_count() - launches0
     fba.check_status(dev)
     ms_local = e0.elapsed_time(e1) / args.steps
@@ -612,7 +613,11 @@ def main():
     # ---------------------------------------------------------------- end to end through the API
     e2e = None
     e2e_checksum = None
+    clocks_e2e = None
     if not args.no_e2e:
+        sampler_e2e = ClockSampler(physical_gpu_index(local_rank))
+        if rank == 0:
+            sampler_e2e.start()
         copy_stream = torch.cuda.Stream(dev)
         back_stream = torch.cuda.Stream(dev)
         # Two sets of device input buffers: while step s computes on one set, the inputs of step
@@ -701,8 +706,8 @@ def main():
         e2e_checksum["note"] = "same, but a 4-float checksum of O,dQ,dK,dV is read back instead of the tensors"
         fba.check_status(dev)
         del bufsets, results_host
+        clocks_e2e = sampler_e2e.stop() if rank == 0 else None
 
-    clocks = sampler.stop() if rank == 0 else None   # sampled over the resident and the end-to-end regions
     total_launches = sum_over_ranks(float(launches))
 
     # ---------------------------------------------------------------- multi-GPU extras
@@ -751,11 +756,12 @@ def main():
                    "pct_of_measured_sustained_peak": 100 * value / (peaks["sustained"] * world),
                    "pct_of_nominal_2250": 100 * value / (2250.0 * world),
                    "work_order": os.environ.get("FBA_WORK_ORDER", "1") != "0"},
-        "e2e": e2e, "e2e_checksum_only": e2e_checksum, "gpu_launches": int(total_launches), "clocks": clocks, "roofline": roofline,
+        "e2e": e2e, "e2e_checksum_only": e2e_checksum, "gpu_launches": int(total_launches), "clocks": clocks,
+        "clocks_e2e": clocks_e2e, "roofline": roofline,
     }
     if clocks and clocks.get("sm_mhz"):
         line["per_clock"] = {"tflops_per_gpu_per_ghz": value / world / (clocks["sm_mhz"] / 1e3),
-                             "note": "value / n_gpus / median SM clock of rank 0 during the timed regions"}
+                             "note": "value / n_gpus / median SM clock of rank 0 during the device-resident timed region"}
     if fp8_fwd is not None:
         line["fp8_fwd"] = fp8_fwd
     if mg_check is not None:

@@ -14,7 +14,8 @@ Differences that a caller can observe:
   * the block mask is compacted once in forward into index lists that backward reuses; the
     reference max-pools the mask (:38-66) and transposes it on every backward (:85-86);
   * ``q_block_size > kv_block_size`` with a 2-D mask works (the reference reshapes it wrongly,
-    :55-57) and a query row that attends to nothing yields a zero output row and zero gradients.
+    :55-57) and a query row that attends to nothing yields a zero output row and zero gradients;
+  * sequences shorter than 128 rows are padded to 128 around the kernels (which want one full tile).
 """
 from __future__ import annotations
 
@@ -700,5 +701,28 @@ def flex_block_attn_func(q, k, v, q_block_size, kv_block_size, block_mask, softm
     Returns:
         [batch, heads, q_seq_len, 128] bf16; differentiable w.r.t. q, k and v.
     """
+    if (q.shape[2] < TILE or k.shape[2] < TILE) and isinstance(block_mask, torch.Tensor):
+        return _short_sequence_call(q, k, v, q_block_size, kv_block_size, block_mask, softmax_scale)
     return FlexBlockAttnFunc.apply(q, k, v, q_block_size, kv_block_size, block_mask, torch.is_grad_enabled(),
                                    softmax_scale)
+
+
+def _short_sequence_call(q, k, v, q_block_size, kv_block_size, block_mask, softmax_scale):
+    """Sequences shorter than one 128-row tile (the reference accepts e.g. one 64-row block,
+    flex_block_attn_interface.py:19; the kernels want at least 128 rows): pad q, k, v with whole zero
+    blocks up to 128 rows, give the added blocks an all-False mask, run, and cut the padding off again.
+    The pad and the slice are torch ops, so gradients flow through them."""
+    Sq, Skv = q.shape[2], k.shape[2]
+    assert Sq % q_block_size == 0, f"q_seq_len ({Sq}) must be divisible by q_block_size ({q_block_size})"
+    assert Skv % kv_block_size == 0, f"kv_seq_len ({Skv}) must be divisible by kv_block_size ({kv_block_size})"
+    Sq2 = Sq if Sq >= TILE else q_block_size * -(-TILE // q_block_size)
+    Skv2 = Skv if Skv >= TILE else kv_block_size * -(-TILE // kv_block_size)
+    pad = torch.nn.functional.pad
+    q2 = pad(q, (0, 0, 0, Sq2 - Sq))
+    k2 = pad(k, (0, 0, 0, Skv2 - Skv))
+    v2 = pad(v, (0, 0, 0, Skv2 - Skv))
+    nQ, nK = block_mask.shape[-2:]
+    m2 = pad(block_mask, (0, Skv2 // kv_block_size - nK, 0, Sq2 // q_block_size - nQ), value=False)
+    out = FlexBlockAttnFunc.apply(q2.contiguous(), k2.contiguous(), v2.contiguous(), q_block_size, kv_block_size,
+                                  m2.contiguous(), torch.is_grad_enabled(), softmax_scale)
+    return out[:, :, :Sq]

@@ -72,3 +72,32 @@ def test_prebuilt_lists_are_checked_against_the_call():
     with pytest.raises(ValueError, match="softmax_scale"):
         lists2 = fba.SparseLists(True, 2, 1, 2, 2, 2, 128, 128, 256, 256, z, c, None, z, c, None)
         fba.flex_block_attn_func(q, k, v, 128, 128, lists2, softmax_scale=float("nan"))
+
+
+def test_bench_reads_roofline_traffic_from_the_committed_profile():
+    """bench.py takes the backward kernel's DRAM bytes per active block pair from the ncu summary
+    under profiles/ (no hand-copied constant)."""
+    import importlib.util
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    spec = importlib.util.spec_from_file_location("bench_mod", root / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    got = bench.bwd_dram_bytes_per_pair()
+    assert got is not None and got[1].startswith("fba_bwd_kernel_")
+    text = (root / "profiles" / got[1]).read_text()
+    assert f"dram_bytes_per_active_pair = {int(got[0])}" in text
+    # the figure is the capture's read + write bytes over its active pairs
+    import re
+    rd = int(re.search(r"dram__bytes_read.sum \| byte \| (\d+)", text).group(1))
+    wr = int(re.search(r"dram__bytes_write.sum \| byte \| (\d+)", text).group(1))
+    pairs = int(re.search(r"([\d ]+) active block pairs\n\n    python bench.py --seq 46080", text).group(1).replace(" ", ""))
+    assert abs((rd + wr) / pairs - got[0]) < 1.0
+    # the step's FLOP count per active pair: 4 + 10 GEMM-flops per (q, kv, d) triple
+    class A:  # minimal stand-in for parsed arguments
+        seq, heads, keep = None, 24, 0.4
+    wl = bench.Workload("c3", A, 24, 0, "cpu")
+    assert wl.flops == 14 * 384 * 384 * 128 and wl.shape == (1, 24, 69120, 128)
+    wl5 = bench.Workload("c5", A, 3, 0, "cpu")
+    assert wl5.flops == 14 * 128 * 384 * 128 and wl5.shape == (2, 3, 69120, 128)
