@@ -101,9 +101,14 @@ def bwd_dram_bytes_per_pair():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason sampling during the timed region (read-only query)."""
+    """nvidia-smi clock / throttle-reason sampling (read-only query), one process for the whole run.
 
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    The process is started long before the first timed region -- its start-up (NVML attaching to every
+    GPU of the machine) takes driver locks that stall kernel launches for a few hundred milliseconds --
+    and every sample carries a timestamp, so that a timed region is summarised afterwards from the
+    samples that fall between its begin() and end() marks."""
+
+    FIELDS = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -111,6 +116,8 @@ class ClockSampler:
         self.gpu_index = gpu_index
         self.proc = None
         self.path = None
+        self.windows = {}
+        self.rows = None
 
     def start(self):
         try:
@@ -122,38 +129,60 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
+    def begin(self, name):
+        self.windows[name] = [time.time(), None]
+
+    def end(self, name):
+        self.windows[name][1] = time.time()
+
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        if self.proc is None or self.rows is not None:
+            return
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, mx, pw, reasons = [], [], [], set()
+        import datetime
+
+        self.rows = []
         try:
             for line in Path(self.path).read_text().splitlines():
                 parts = [x.strip() for x in line.split(",")]
-                if len(parts) < 9:
+                if len(parts) < 10:
                     continue
                 try:
-                    sm.append(float(parts[1]))
-                    mx.append(float(parts[2]))
+                    t = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    self.rows.append((t, float(parts[2]), float(parts[3]), parts[4], parts[6:10]))
                 except ValueError:
                     continue
-                try:
-                    pw.append(float(parts[3]))
-                except ValueError:
-                    pass
-                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
-                    if val.lower().startswith("active"):
-                        reasons.add(name)
             os.unlink(self.path)
         except Exception:
             pass
-        if not sm:
+
+    def summary(self, name):
+        """Median SM clock, maximum clock, throttle reasons and median power over one window."""
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        self.stop()
+        t0, t1 = self.windows[name]
+        rows = [r for r in self.rows if t0 <= r[0] <= t1]
+        if not rows:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no_samples"]}
-        out = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        reasons = set()
+        for r in rows:
+            for nm, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[4]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        out = {"sm_mhz": statistics.median(r[1] for r in rows), "sm_max_mhz": max(r[2] for r in rows),
+               "reasons": sorted(reasons), "samples": len(rows)}
+        pw = []
+        for r in rows:
+            try:
+                pw.append(float(r[3]))
+            except ValueError:
+                pass
         if pw:
             out["power_w"] = statistics.median(pw)
         return out
@@ -534,30 +563,35 @@ def main():
     # One-time set-up that is not a step: first-call initialisation (module load, shared-memory
     # attribute, tensor-map encoder lookup) and growth of torch's caching allocator to the working
     # set, so that the W warm-up steps and the K timed steps all run in steady state.
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    if rank == 0:
+        sampler.start()
+    # (`keep` holds a step's outputs until the next step has produced its own, exactly as the timed
+    # loop does: with a shorter lifetime here the timed loop's peak would be higher than the warm-up's
+    # and the allocator would call cudaMalloc -- a device-wide synchronisation -- inside the timed region.)
+    keep = None
     for i in range(2):
-        step_resident(-1 - i)
+        keep = step_resident(-1 - i)
     torch.cuda.synchronize()
     for i in range(args.warmup):
-        step_resident(i)
+        keep = step_resident(i)
     hooks = []
     for _ in range(args.steps):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record(); b.record()
         hooks.append((a, b))
-    sampler = ClockSampler(physical_gpu_index(local_rank))
     barrier()
-    if rank == 0:
-        sampler.start()
+    sampler.begin("resident")
     launches0 = lib.fba_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     pairs_seen = []
     for i in range(args.steps):
-        p, _ = step_resident(args.warmup + i, hooks[i])
-        pairs_seen.append(p)
+        keep = step_resident(args.warmup + i, hooks[i])
+        pairs_seen.append(keep[0])
     e1.record()
     barrier()
-    clocks = sampler.stop() if rank == 0 else None     # sampled over the device-resident timed region only
+    sampler.end("resident")
     launches = lib.fba_launch_count() - launches0
     fba.check_status(dev)
     ms_local = e0.elapsed_time(e1) / args.steps
@@ -566,7 +600,7 @@ def main():
     nnz = sum_over_ranks(nnz_local)
     value = nnz * wl.flops / (ms / 1e3) / 1e12
     bwd_ms = statistics.mean(a.elapsed_time(b) for a, b in hooks)
-    del pairs_seen
+    del pairs_seen, keep
 
     # forward main kernel alone, a few extra steps (reported beside the roofline object)
     fwd_ms = None
@@ -613,11 +647,8 @@ def main():
     # ---------------------------------------------------------------- end to end through the API
     e2e = None
     e2e_checksum = None
-    clocks_e2e = None
     if not args.no_e2e:
-        sampler_e2e = ClockSampler(physical_gpu_index(local_rank))
-        if rank == 0:
-            sampler_e2e.start()
+        sampler.begin("e2e")
         copy_stream = torch.cuda.Stream(dev)
         back_stream = torch.cuda.Stream(dev)
         # Two sets of device input buffers: while step s computes on one set, the inputs of step
@@ -706,8 +737,13 @@ def main():
         e2e_checksum["note"] = "same, but a 4-float checksum of O,dQ,dK,dV is read back instead of the tensors"
         fba.check_status(dev)
         del bufsets, results_host
-        clocks_e2e = sampler_e2e.stop() if rank == 0 else None
+        sampler.end("e2e")
 
+    clocks = clocks_e2e = None
+    if rank == 0:
+        clocks = sampler.summary("resident")      # the device-resident timed region only
+        if "e2e" in sampler.windows:
+            clocks_e2e = sampler.summary("e2e")
     total_launches = sum_over_ranks(float(launches))
 
     # ---------------------------------------------------------------- multi-GPU extras

@@ -220,7 +220,7 @@ def test_inference_forward_skips_lse():
         fba.flex_block_attn_func(q, k, v, 384, 384, mask, softmax_scale=-1.0)
 
 
-@pytest.mark.parametrize("Sq,Skv,qb,kb", [(64, 64, 64, 64), (64, 64, 16, 64), (64, 256, 32, 64), (256, 64, 128, 64), (96, 192, 48, 64)])
+@pytest.mark.parametrize("Sq,Skv,qb,kb", [(64, 64, 64, 64), (64, 64, 16, 64), (64, 256, 32, 64), (256, 64, 128, 64), (96, 192, 48, 192)])
 def test_sequences_shorter_than_one_tile(Sq, Skv, qb, kb):
     """The reference accepts a sequence of one 64-row block (flex_block_attn_interface.py:19); the
     Python layer pads such inputs to one 128-row tile around the kernels."""
