@@ -152,9 +152,9 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
     if (warp >= 8) {
         // Register pool of the CTA = 384 threads x 168 at launch = 3 x 128 x 168.  The budgets set
-        // below must not add up to more than that (200 + 200 + 96 <= 504), or the increase would
+        // below must not add up to more than that (216 + 216 + 72 = 504), or the increase would
         // wait for registers that are never released.
-        reg_dec<96>();
+        reg_dec<72>();
         if (warp == 9) {
             // -------------------------------------------------------------- TMA loader
             if (lane == 0) {
@@ -299,7 +299,7 @@ fba_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
     } else {
         // ------------------------------------------------------------------ softmax + epilogue
-        reg_inc<200>();
+        reg_inc<216>();
         const int t = warp >> 2;                       // 0: tile A, 1: tile B
         const int row = (warp & 3) * 32 + lane;        // row inside the tile == TMEM lane
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;

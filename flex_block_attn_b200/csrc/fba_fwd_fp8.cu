@@ -126,7 +126,7 @@ fba_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     };
 
     if (warp >= 8) {
-        reg_dec<96>();
+        reg_dec<72>();
         if (warp == 9) {
             // -------------------------------------------------------------- TMA loader
             if (lane == 0) {
@@ -256,7 +256,7 @@ fba_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
     } else {
         // ------------------------------------------------------------------ softmax + epilogue
-        reg_inc<200>();
+        reg_inc<216>();
         const int t = warp >> 2;
         const int row = (warp & 3) * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
