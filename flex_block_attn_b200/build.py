@@ -6,7 +6,10 @@ there is one target and no third-party headers: every ``csrc/*.cu`` is compiled 
 ``-gencode arch=compute_100a,code=sm_100a`` and linked into one shared library next to this file.
 
 Run ``python -m flex_block_attn_b200.build`` (add ``--force`` to rebuild, ``--verbose`` for the
-ptxas register / shared-memory report).
+ptxas register / shared-memory report).  ``FBA_NVCC_EXTRA`` in the environment appends flags to
+every compile, e.g. ``FBA_NVCC_EXTRA="-DFBA_RED_SLEEP_NS=16" python -m flex_block_attn_b200.build
+--force`` for an A/B of one of the kernels' compile-time tuning constants (``FBA_RED_SLEEP_NS``,
+``FBA_BWD_PREFETCH``, ``FBA_FWD_POLY_PAIRS``, ``FBA_TRACE``).
 """
 from __future__ import annotations
 
@@ -58,7 +61,7 @@ def is_stale() -> bool:
 
 def _compile_one(nvcc: str, src: Path, verbose: bool) -> tuple[Path, str]:
     obj = OBJ_DIR / (src.stem + ".o")
-    cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+    cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("FBA_NVCC_EXTRA", "").split(), "-c", str(src), "-o", str(obj)]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     r = subprocess.run(cmd, capture_output=True, text=True)
