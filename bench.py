@@ -716,7 +716,7 @@ def main():
         def measure(full_results):
             run_e2e(0, max(2, min(args.warmup, 3)), full_results)
             barrier()
-            n_e2e = max(2, min(args.steps, 10))
+            n_e2e = max(2, min(args.steps, 20))
             t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             t0.record()
             seen = run_e2e(100, n_e2e, full_results)
