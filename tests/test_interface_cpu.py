@@ -101,3 +101,18 @@ def test_bench_reads_roofline_traffic_from_the_committed_profile():
     assert wl.flops == 14 * 384 * 384 * 128 and wl.shape == (1, 24, 69120, 128)
     wl5 = bench.Workload("c5", A, 3, 0, "cpu")
     assert wl5.flops == 14 * 128 * 384 * 128 and wl5.shape == (2, 3, 69120, 128)
+
+
+def test_compat_module_has_the_reference_extension_signatures():
+    """flex_block_attn_b200.compat stands in for the reference's compiled module: same two names, same
+    positional parameters as attention_forward / attention_backward (reference attn.cpp:12-21)."""
+    import inspect
+
+    from flex_block_attn_b200 import compat
+
+    fwd = list(inspect.signature(compat.attn_forward).parameters)
+    bwd = list(inspect.signature(compat.attn_backward).parameters)
+    assert fwd == ["q", "k", "v", "q_block_size", "kv_block_size", "load_block_mask", "compute_block_mask",
+                   "use_small_block_mode"]
+    assert bwd == ["q", "k", "v", "o", "l_vec", "og", "q_block_size", "kv_block_size", "load_block_mask",
+                   "compute_block_mask", "use_small_block_mode"]
