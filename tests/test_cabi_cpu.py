@@ -113,6 +113,12 @@ def test_list_geometry_is_checked_before_any_device_work(lib):
     args[17] = 1   # FBA_DQ_QMAJOR without a q2k list
     assert lib.fba_bwd_ex(*args) == -1 and b"q2k" in lib.fba_last_error()
     assert lib.fba_set_bwd_kernel(0) == -1
+    # the work order refuses more items per (batch, head) than its shared-memory sort holds; callers then
+    # leave `order` NULL (the Python layer does)
+    big = FbaList(0x1000, 0x1000, None, 16, 13000, 13000, 1, 1)
+    assert lib.fba_bwd_order(ctypes.byref(big), 1, 1, 1, 13000 * 128, fake, None) == -5
+    assert b"12288" in lib.fba_last_error()
+    assert lib.fba_fwd_order(ctypes.byref(big), 1, 1, 2 * 12288 * 128, fake, None) == -1   # list does not cover Sq
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
