@@ -620,6 +620,24 @@ def main():
     except Exception:
         lib.fba_set_timing_events(0, None, None)
 
+    # mask draw + compaction (both directions) + work orders, timed alone (it is inside every step)
+    lists_ms = None
+    try:
+        evs = []
+        for i in range(6):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            l, _, _ = wl.lists(fba, masks, 1000 + i, q, k)
+            l.fwd_list(ordered=True)
+            l.bwd_list(Hl, Hl)
+            b.record()
+            evs.append((a, b))
+        torch.cuda.synchronize()
+        lists_ms = statistics.median(a.elapsed_time(b) for a, b in evs[1:])
+        del l
+    except Exception:
+        pass
+
     # inference forward over an e4m3 key / value cache, same lists (optional)
     fp8_fwd = None
     if args.fp8:
@@ -798,6 +816,10 @@ def main():
     if clocks and clocks.get("sm_mhz"):
         line["per_clock"] = {"tflops_per_gpu_per_ghz": value / world / (clocks["sm_mhz"] / 1e3),
                              "note": "value / n_gpus / median SM clock of rank 0 during the device-resident timed region"}
+    line["breakdown_ms"] = {"mask_lists_order": lists_ms, "fwd_kernel_alone": fwd_ms, "bwd_main_kernel_in_step": bwd_ms,
+                            "step": ms_local,
+                            "note": "mask draw / list building + compaction + work orders timed alone with CUDA events (median of 5); "
+                                    "forward kernel alone after the timed loop; backward main kernel inside the timed steps"}
     if fp8_fwd is not None:
         line["fp8_fwd"] = fp8_fwd
     if mg_check is not None:
